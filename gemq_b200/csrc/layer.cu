@@ -1,0 +1,144 @@
+// One-token forward of a quantised MoE layer: router, fused gate/up projection,
+// SiLU*mul + down projection with the top-k combine folded into its epilogue.
+// Three launches, no host involvement between them.
+#include "gemv.cuh"
+
+namespace gemq {
+
+struct DecodeScratch {
+  void* gemv_ws;
+  size_t gemv_ws_bytes;
+  __half* x1;  // [A*F + shared_ffn]
+  __half* x3;
+};
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static size_t decode_ws_bytes(const gemq_moe_layer_t* L) {
+  const int up_cols = 2 * (L->top_k * L->ffn + L->shared_ffn);
+  const int down_cols = (L->top_k + (L->shared_ffn > 0 ? 1 : 0)) * L->hidden;
+  const int max_k = L->ffn > L->hidden ? L->ffn : L->hidden;
+  const int mk = L->shared_ffn > max_k ? L->shared_ffn : max_k;
+  return align_up(gemv_workspace_bytes(up_cols > down_cols ? up_cols : down_cols, mk, 1), 256);
+}
+
+static bool carve(const gemq_moe_layer_t* L, void* scratch, size_t bytes, DecodeScratch* S) {
+  const size_t ws = decode_ws_bytes(L);
+  const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(__half), 256);
+  if (!scratch || bytes < ws + 2 * act || !aligned16(scratch)) return false;
+  char* p = static_cast<char*>(scratch);
+  S->gemv_ws = p;
+  S->gemv_ws_bytes = ws;
+  S->x1 = reinterpret_cast<__half*>(p + ws);
+  S->x3 = reinterpret_cast<__half*>(p + ws + act);
+  return true;
+}
+
+static void stacked_job(GemvJob& J, const gemq_stacked_t& W, const int64_t* idx_slot, int N, int K) {
+  J.wq = reinterpret_cast<const uint32_t*>(W.wq);
+  J.scales = static_cast<const __half*>(W.scales);
+  J.zeros = static_cast<const __half*>(W.zeros);
+  J.nbits = W.nbits;
+  J.wq_strides = W.wq_strides;
+  J.zs_strides = W.zs_strides;
+  J.idx = reinterpret_cast<const long long*>(idx_slot);
+  J.N = N;
+  J.K = K;
+}
+
+static void single_job(GemvJob& J, const gemq_single_t& W, int N, int K) {
+  J.wq = reinterpret_cast<const uint32_t*>(W.wq);
+  J.scales = static_cast<const __half*>(W.scales);
+  J.zeros = static_cast<const __half*>(W.zeros);
+  J.fixed_bits = W.nbits;
+  J.N = N;
+  J.K = K;
+}
+
+}  // namespace gemq
+
+using namespace gemq;
+
+extern "C" size_t gemq_moe_decode_scratch_bytes(const gemq_moe_layer_t* L) {
+  if (!L || L->hidden <= 0 || L->ffn <= 0 || L->top_k <= 0) return 0;
+  const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(__half), 256);
+  return decode_ws_bytes(L) + 2 * act;
+}
+
+extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* out,
+                               int64_t* idx, void* w, int tokens, int do_route, int route_mode,
+                               void* scratch, size_t scratch_bytes, gemq_stream_t stream) {
+  if (!L || !x || !out || !idx || !w || !L->gate || tokens <= 0) return GEMQ_ERR_BAD_ARG;
+  const int D = L->hidden, F = L->ffn, A = L->top_k, SF = L->shared_ffn;
+  if (D <= 0 || F <= 0 || A <= 0 || A > kMaxSlots || L->n_experts <= 0 || SF < 0) return GEMQ_ERR_BAD_ARG;
+  if (L->group_size != kGroup || D % kGroup || F % kGroup || SF % kGroup) return GEMQ_ERR_BAD_SHAPE;
+  if (SF > 0 && (L->s1.group_size != kGroup || L->s3.group_size != kGroup || L->s2.group_size != kGroup))
+    return GEMQ_ERR_BAD_SHAPE;
+  DecodeScratch S;
+  if (!carve(L, scratch, scratch_bytes, &S)) return GEMQ_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (do_route) {
+    const int rc = gemq_moe_route(x, L->gate, tokens, D, L->n_experts, A, route_mode, L->renorm, 0, idx, w, nullptr,
+                                  stream);
+    if (rc) return rc;
+  }
+
+  for (int t = 0; t < tokens; ++t) {
+    const __half* xt = static_cast<const __half*>(x) + static_cast<size_t>(t) * D;
+    const int64_t* idx_t = idx + static_cast<size_t>(t) * A;
+    // gate / up projections: x1[a*F + f], x3[a*F + f]; shared experts behind the routed slots
+    GemvParams P = {};
+    P.T = 1;
+    int nj = 0;
+    for (int a = 0; a < A; ++a) {
+      for (int m = 0; m < 2; ++m) {
+        GemvJob& J = P.jobs[nj++];
+        stacked_job(J, m ? L->w3 : L->w1, idx_t + a, F, D);
+        if (m) {  // w1 and w3 share bit-widths and word offsets (fused_dequant_bmm.py:56-57)
+          J.nbits = L->w1.nbits;
+          J.wq_strides = L->w1.wq_strides;
+        }
+        J.xa = xt;
+        J.ldx = D;
+        J.y = (m ? S.x3 : S.x1) + static_cast<size_t>(a) * F;
+      }
+    }
+    if (SF > 0) {
+      for (int m = 0; m < 2; ++m) {
+        GemvJob& J = P.jobs[nj++];
+        single_job(J, m ? L->s3 : L->s1, SF, D);
+        J.xa = xt;
+        J.ldx = D;
+        J.y = (m ? S.x3 : S.x1) + static_cast<size_t>(A) * F;
+      }
+    }
+    P.n_jobs = nj;
+    int rc = run_gemv_jobs(P, false, kGroup, S.gemv_ws, S.gemv_ws_bytes, st);
+    if (rc) return rc;
+
+    // down projection + combine
+    GemvParams Q = {};
+    Q.T = 1;
+    nj = 0;
+    for (int a = 0; a < A; ++a) {
+      GemvJob& J = Q.jobs[nj++];
+      stacked_job(J, L->w2, idx_t + a, D, F);
+      J.xa = S.x1 + static_cast<size_t>(a) * F;
+      J.xb = S.x3 + static_cast<size_t>(a) * F;
+    }
+    if (SF > 0) {
+      GemvJob& J = Q.jobs[nj++];
+      single_job(J, L->s2, D, SF);
+      J.xa = S.x1 + static_cast<size_t>(A) * F;
+      J.xb = S.x3 + static_cast<size_t>(A) * F;
+    }
+    Q.n_jobs = nj;
+    Q.comb_out = static_cast<__half*>(out) + static_cast<size_t>(t) * D;
+    Q.comb_w = static_cast<const __half*>(w) + static_cast<size_t>(t) * A;
+    Q.comb_weighted = A;
+    rc = run_gemv_jobs(Q, true, kGroup, S.gemv_ws, S.gemv_ws_bytes, st);
+    if (rc) return rc;
+  }
+  return GEMQ_OK;
+}

@@ -1,0 +1,145 @@
+// Router: gate GEMV, softmax, top-k and renormalisation in one launch, one CTA per token.
+// Results stay on the device (expert ids as int64, like torch.topk returns them).
+#include "common.cuh"
+
+namespace gemq {
+
+constexpr int kRouteThreads = 256;
+constexpr int kRouteMaxExperts = 256;
+constexpr int kRouteMaxTopK = 16;
+
+template <typename T> struct Act;
+template <> struct Act<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Act<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+template <typename T>
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
+  const T* pa = reinterpret_cast<const T*>(&a);
+  const T* pb = reinterpret_cast<const T*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s = fmaf(Act<T>::to_f(pa[i]), Act<T>::to_f(pb[i]), s);
+  return s;
+}
+
+// mode 0: logits, probabilities, their sum and the quotient are each rounded to the
+//         activation dtype (softmax/topk/renorm of a half tensor);
+// mode 1: logits rounded to the activation dtype, softmax and renormalisation in fp32;
+// mode 2: fp32 throughout.  The returned weights are cast to the activation dtype.
+template <typename T>
+__global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restrict__ x, const T* __restrict__ gate,
+                                                              int D, int E, int A, int mode, int renorm,
+                                                              long long* __restrict__ idx, T* __restrict__ weights,
+                                                              float* __restrict__ logits_out) {
+  __shared__ float logit[kRouteMaxExperts];
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* xt = x + static_cast<size_t>(t) * D;
+  const bool vec = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(xt) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(gate) & 15u) == 0);
+  for (int e = warp; e < E; e += kRouteThreads / 32) {
+    const T* ge = gate + static_cast<size_t>(e) * D;
+    float s = 0.f;
+    if (vec) {
+      for (int k = lane * 8; k < D; k += 256)
+        s += dot8<T>(*reinterpret_cast<const uint4*>(xt + k), *reinterpret_cast<const uint4*>(ge + k));
+    } else {
+      for (int k = lane; k < D; k += 32) s = fmaf(Act<T>::to_f(xt[k]), Act<T>::to_f(ge[k]), s);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+      if (mode != 2) s = Act<T>::to_f(Act<T>::from_f(s));
+      logit[e] = s;
+      if (logits_out) logits_out[static_cast<size_t>(t) * E + e] = s;
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+
+  constexpr int PER = kRouteMaxExperts / 32;
+  float p[PER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    p[i] = e < E ? logit[e] : -INFINITY;
+    mx = fmaxf(mx, p[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    p[i] = (lane + 32 * i) < E ? expf(p[i] - mx) : 0.f;
+    sum += p[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    p[i] = p[i] / sum;
+    if (mode == 0) p[i] = Act<T>::to_f(Act<T>::from_f(p[i]));
+    if ((lane + 32 * i) >= E) p[i] = -1.f;
+  }
+  // top-k: A rounds of warp arg-max, ties to the lower expert id
+  float wsel[kRouteMaxTopK];
+  int isel[kRouteMaxTopK];
+  for (int a = 0; a < A; ++a) {
+    float bv = -2.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (p[i] > bv) { bv = p[i]; bi = lane + 32 * i; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    wsel[a] = bv;
+    isel[a] = bi;
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (lane + 32 * i == bi) p[i] = -3.f;
+  }
+  if (lane == 0) {
+    float tot = 0.f;
+    for (int a = 0; a < A; ++a) tot += wsel[a];
+    if (mode == 0) tot = Act<T>::to_f(Act<T>::from_f(tot));
+    for (int a = 0; a < A; ++a) {
+      float w = wsel[a];
+      if (renorm) w = w / tot;
+      idx[static_cast<size_t>(t) * A + a] = isel[a];
+      weights[static_cast<size_t>(t) * A + a] = Act<T>::from_f(w);
+    }
+  }
+}
+
+}  // namespace gemq
+
+using namespace gemq;
+
+extern "C" int gemq_moe_route(const void* x, const void* gate, int tokens, int D, int E, int A,
+                              int mode, int renorm, int x_is_bf16,
+                              int64_t* idx, void* weights, float* logits, gemq_stream_t stream) {
+  if (!x || !gate || !idx || !weights || tokens <= 0 || D <= 0 || E <= 0 || A <= 0 || mode < 0 || mode > 2)
+    return GEMQ_ERR_BAD_ARG;
+  if (E > kRouteMaxExperts || A > kRouteMaxTopK || A > E) return GEMQ_ERR_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (x_is_bf16)
+    route_kernel<__nv_bfloat16><<<tokens, kRouteThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate), D, E, A, mode, renorm,
+        reinterpret_cast<long long*>(idx), static_cast<__nv_bfloat16*>(weights), logits);
+  else
+    route_kernel<__half><<<tokens, kRouteThreads, 0, s>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(gate), D, E, A, mode, renorm,
+        reinterpret_cast<long long*>(idx), static_cast<__half*>(weights), logits);
+  return launch_status();
+}

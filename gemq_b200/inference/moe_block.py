@@ -1,0 +1,275 @@
+"""Quantised fused MoE blocks for Mixtral and DeepSeek-V2 on the gemq_b200 kernels.
+
+Same constructor / ``from_hf`` / ``forward`` surface and attribute names as
+``QuantFusedMixtralMoEBlock`` and ``QuantFusedDeepseekV2MoEBlock`` in
+gemq/inference/moe_block.py, so ``replace_moe_blocks`` (gemq/inference/patch.py:82-125)
+can swap them in.  A one-token forward is a single library call (router, fused
+gate/up, SiLU*mul + down, combine); the routing result never reaches the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+
+from .. import _capi
+from ..kernels import dequant_gemm, dequant_group_gemm
+from ..kernels._runtime import require_cuda, stream_ptr
+from .packed_linear import is_packed_linear
+
+ROUTE_FP16, ROUTE_FP32_SOFTMAX, ROUTE_FP32 = 0, 1, 2
+_MAX_LOOPED_TOKENS = 16
+
+
+def _excl_cumsum(vals, device):
+    t = torch.tensor([0] + list(vals), dtype=torch.int64).cumsum(0)[:-1]
+    assert int(t.max()) < 2 ** 31, "stacked tensor too large for int32 offsets"
+    return t.to(torch.int32).to(device)
+
+
+class _QuantFusedMoEBase(nn.Module):
+    """State and dispatch shared by the two model families."""
+
+    _projections = ("w1", "w2", "w3")
+
+    def __init__(self) -> None:
+        super().__init__()
+        for p in self._projections:
+            for suffix in ("wq", "scales", "zeros", "nbits", "group_sizes", "wq_strides", "zs_strides"):
+                setattr(self, f"{p}_{suffix}", None)
+        self.block_group_size = None
+        self._layer = None       # ctypes struct handed to the library
+        self._scratch = None
+        self._nbits_host = None
+
+    # -- construction ---------------------------------------------------------------
+    def _stack(self, name: str, linears) -> None:
+        """Concatenate per-expert packed tensors and build the metadata tensors
+        (gemq/inference/moe_block.py:111-142)."""
+        dev = linears[0].W_q.device
+        setattr(self, f"{name}_wq", torch.cat([l.W_q.data.contiguous() for l in linears]))
+        setattr(self, f"{name}_scales", torch.cat([l.scales.data for l in linears]).contiguous())
+        setattr(self, f"{name}_zeros", torch.cat([l.zeros.data for l in linears]).contiguous())
+        setattr(self, f"{name}_nbits", torch.tensor([l.W_nbits for l in linears], dtype=torch.int32, device=dev))
+        setattr(self, f"{name}_group_sizes",
+                torch.tensor([l.group_size for l in linears], dtype=torch.int32, device=dev))
+        setattr(self, f"{name}_wq_strides", _excl_cumsum([l.W_q.numel() for l in linears], dev))
+        setattr(self, f"{name}_zs_strides", _excl_cumsum([l.scales.numel() for l in linears], dev))
+
+    def _check_group_sizes(self, experts_w1, experts_w2, experts_w3) -> None:
+        sizes = {l.group_size for l in (*experts_w1, *experts_w2, *experts_w3)}
+        assert len(sizes) == 1, "Group sizes must be the same across all experts."
+        self.block_group_size = int(sizes.pop())
+        bits = [(a.W_nbits, b.W_nbits) for a, b in zip(experts_w1, experts_w3)]
+        assert all(a == b for a, b in bits), "w1 and w3 of an expert must share a bit-width"
+        self._nbits_host = [int(l.W_nbits) for l in experts_w1]
+
+    def _stacked_struct(self, name: str) -> _capi.Stacked:
+        g = lambda s: getattr(self, f"{name}_{s}").data_ptr()
+        return _capi.Stacked(g("wq"), g("scales"), g("zeros"), g("nbits"), g("wq_strides"), g("zs_strides"))
+
+    def _single_struct(self, name: str) -> _capi.Single:
+        g = lambda s: getattr(self, f"shared_{name}_{s}").data_ptr()
+        return _capi.Single(g("wq"), g("scales"), g("zeros"), int(self.shared_nbits), int(self.shared_group_size))
+
+    def _build_layer(self, route_mode: int, renorm: bool, shared_ffn: int) -> None:
+        dev = self.w1_wq.device
+        self.gate.to(device=dev, dtype=torch.float16)
+        L = _capi.MoeLayer()
+        L.hidden, L.ffn, L.n_experts, L.top_k = self.hidden_dim, self.ffn_dim, self.num_experts, self.top_k
+        L.group_size, L.route_mode, L.renorm, L.shared_ffn = self.block_group_size, route_mode, int(renorm), shared_ffn
+        L.gate = self.gate.weight.data_ptr()
+        L.w1, L.w3, L.w2 = self._stacked_struct("w1"), self._stacked_struct("w3"), self._stacked_struct("w2")
+        if shared_ffn:
+            L.s1, L.s3, L.s2 = self._single_struct("w1"), self._single_struct("w3"), self._single_struct("w2")
+        self._layer = L
+        nbytes = _capi.lib.gemq_moe_decode_scratch_bytes(C.byref(L))
+        self._scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+
+    # -- forward pieces ----------------------------------------------------------------
+    def _decode(self, x: Tensor, route_mode: int):
+        """``x [T, D]`` fp16 -> ``out [T, D]``, routing weights and indices, all on the device."""
+        dev = require_cuda(x)
+        T = x.shape[0]
+        out = torch.empty_like(x)
+        idx = torch.empty((T, self.top_k), dtype=torch.int64, device=dev)
+        w = torch.empty((T, self.top_k), dtype=torch.float16, device=dev)
+        _capi.check("gemq_moe_decode", _capi.lib.gemq_moe_decode(
+            C.byref(self._layer), x.data_ptr(), out.data_ptr(), idx.data_ptr(), w.data_ptr(), T, 1, route_mode,
+            self._scratch.data_ptr(), self._scratch.numel(), stream_ptr(dev)))
+        return out, w, idx
+
+    def _route(self, x: Tensor, mode: int, renorm: bool):
+        dev = require_cuda(x)
+        T, D = x.shape
+        idx = torch.empty((T, self.top_k), dtype=torch.int64, device=dev)
+        w = torch.empty((T, self.top_k), dtype=x.dtype, device=dev)
+        logits = torch.empty((T, self.num_experts), dtype=torch.float32, device=dev)
+        gate = self.gate.weight if x.dtype == torch.float16 else self.gate.weight.to(x.dtype)
+        _capi.check("gemq_moe_route", _capi.lib.gemq_moe_route(
+            x.data_ptr(), gate.data_ptr(), T, D, self.num_experts, self.top_k, mode, int(renorm),
+            int(x.dtype == torch.bfloat16), idx.data_ptr(), w.data_ptr(), logits.data_ptr(), stream_ptr(dev)))
+        return w, idx, logits
+
+    def forward_single_expert(self, expert_idx: Tensor, hidden_states: Tensor) -> Tensor:
+        """Expert FFN on ``[T, D]`` rows (gemq/inference/moe_block.py:146-163)."""
+        x = hidden_states
+        x1 = dequant_group_gemm(x, expert_idx, self.w1_wq, self.w1_scales, self.w1_zeros,
+                                self.w1_nbits, self.w1_group_sizes, self.w1_wq_strides, self.w1_zs_strides)[0]
+        x3 = dequant_group_gemm(x, expert_idx, self.w3_wq, self.w3_scales, self.w3_zeros,
+                                self.w3_nbits, self.w3_group_sizes, self.w3_wq_strides, self.w3_zs_strides)[0]
+        return dequant_group_gemm(F.silu(x1) * x3, expert_idx, self.w2_wq, self.w2_scales, self.w2_zeros,
+                                  self.w2_nbits, self.w2_group_sizes, self.w2_wq_strides, self.w2_zs_strides)[0]
+
+    def _experts_n_tokens(self, x: Tensor, routing_weights: Tensor, selected: Tensor) -> Tensor:
+        """Per-expert gather / FFN / weighted scatter-add of the n-token path
+        (gemq/inference/moe_block.py:182-195)."""
+        xh = x if x.dtype == torch.float16 else x.to(torch.float16)
+        final = torch.zeros_like(x)
+        expert_mask = F.one_hot(selected, num_classes=self.num_experts).permute(2, 1, 0)
+        expert_hit = torch.greater(expert_mask.sum(dim=(-1, -2)), 0).nonzero()
+        for expert_idx in expert_hit:
+            slot, top_x = torch.where(expert_mask[expert_idx].squeeze(0))
+            cur = self.forward_single_expert(expert_idx, xh[top_x]).to(x.dtype) * routing_weights[top_x, slot, None]
+            final.index_add_(0, top_x, cur.to(x.dtype))
+        return final
+
+
+class QuantFusedMixtralMoEBlock(_QuantFusedMoEBase):
+    """Drop-in for gemq/inference/moe_block.py:73-240."""
+
+    def __init__(self, config) -> None:
+        super().__init__()
+        self.hidden_dim = config.hidden_size
+        self.ffn_dim = config.intermediate_size
+        self.num_experts = config.num_local_experts
+        self.top_k = config.num_experts_per_tok
+        self.gate = nn.Linear(self.hidden_dim, self.num_experts, bias=False)
+
+    @classmethod
+    def from_hf(cls, config, hf_block):
+        experts = list(hf_block.experts)
+        if not is_packed_linear(experts[0].w1):
+            raise ValueError("Expected linears in MixtralSparseMoeBlock. Please patch and replace them first.")
+        return cls.from_linears(config, hf_block.gate.weight.data,
+                                [e.w1 for e in experts], [e.w2 for e in experts], [e.w3 for e in experts])
+
+    @classmethod
+    def from_linears(cls, config, gate_weight: Tensor, w1, w2, w3):
+        """Build from per-expert packed linears (lists of length ``num_local_experts``)."""
+        blk = cls(config)
+        blk.gate.weight.data = gate_weight.detach().clone()
+        blk._check_group_sizes(w1, w2, w3)
+        blk._stack("w1", w1)
+        blk._stack("w2", w2)
+        blk._stack("w3", w3)
+        blk._build_layer(ROUTE_FP16, True, 0)
+        return blk
+
+    def forward_n_tokens(self, hidden_states: Tensor):
+        """gemq/inference/moe_block.py:165-198."""
+        b, s, d = hidden_states.shape
+        x = hidden_states.reshape(-1, d)
+        rw, sel, logits = self._route(x, ROUTE_FP32_SOFTMAX, True)
+        out = self._experts_n_tokens(x, rw, sel)
+        return out.reshape(b, s, d), logits.to(hidden_states.dtype)
+
+    def forward_one_token(self, hidden_states: Tensor):
+        """gemq/inference/moe_block.py:200-235."""
+        b, s, d = hidden_states.shape
+        x = hidden_states.reshape(-1, self.hidden_dim)
+        assert x.shape[0] == 1, f"This function only supports single token forward. But got {x.shape[0]} tokens."
+        xh = x if x.dtype == torch.float16 else x.to(torch.float16)
+        out, _, _ = self._decode(xh.contiguous(), ROUTE_FP16)
+        return out.to(hidden_states.dtype).reshape(b, s, d), None
+
+    def forward(self, hidden_states: Tensor):
+        if hidden_states.shape[0] == hidden_states.shape[1] == 1:
+            return self.forward_one_token(hidden_states)
+        return self.forward_n_tokens(hidden_states)
+
+
+class QuantFusedDeepseekV2MoEBlock(_QuantFusedMoEBase):
+    """Drop-in for gemq/inference/moe_block.py:321-536."""
+
+    def __init__(self, config) -> None:
+        super().__init__()
+        self.hidden_dim = config.hidden_size
+        self.ffn_dim = config.moe_intermediate_size
+        self.num_experts = config.n_routed_experts
+        self.num_shared_experts = config.n_shared_experts
+        self.top_k = config.num_experts_per_tok
+        self.norm_topk_prob = config.norm_topk_prob
+        self.gate = nn.Linear(self.hidden_dim, self.num_experts, bias=False)
+        for p in self._projections:
+            for suffix in ("wq", "scales", "zeros"):
+                setattr(self, f"shared_{p}_{suffix}", None)
+        self.shared_nbits, self.shared_group_size = None, None
+
+    @classmethod
+    def from_hf(cls, config, hf_block):
+        experts = list(hf_block.experts)
+        if not is_packed_linear(experts[0].gate_proj):
+            raise ValueError("Expected linears in DeepseekV2MoE. Please patch and replace them first.")
+        sh = hf_block.shared_experts
+        return cls.from_linears(config, hf_block.gate.weight.data,
+                                [e.gate_proj for e in experts], [e.down_proj for e in experts],
+                                [e.up_proj for e in experts], (sh.gate_proj, sh.down_proj, sh.up_proj))
+
+    @classmethod
+    def from_linears(cls, config, gate_weight: Tensor, w1, w2, w3, shared):
+        """``shared`` = (gate_proj, down_proj, up_proj) packed linears of the merged shared experts."""
+        blk = cls(config)
+        blk.gate.weight.data = gate_weight.detach().clone()
+        blk._check_group_sizes(w1, w2, w3)
+        blk._stack("w1", w1)
+        blk._stack("w2", w2)
+        blk._stack("w3", w3)
+        s1, s2, s3 = shared
+        for name, lin in (("w1", s1), ("w2", s2), ("w3", s3)):
+            setattr(blk, f"shared_{name}_wq", lin.W_q.data.contiguous().clone())
+            setattr(blk, f"shared_{name}_scales", lin.scales.data.contiguous().clone())
+            setattr(blk, f"shared_{name}_zeros", lin.zeros.data.contiguous().clone())
+        # the shared projections are assumed to share nbits and group size (moe_block.py:410-412)
+        blk.shared_nbits, blk.shared_group_size = int(s1.W_nbits), int(s1.group_size)
+        blk._build_layer(ROUTE_FP32, bool(blk.norm_topk_prob), blk.shared_w1_wq.shape[1])
+        return blk
+
+    def _shared_ffn(self, x: Tensor) -> Tensor:
+        """gemq/inference/moe_block.py:419-430."""
+        b, g = self.shared_nbits, self.shared_group_size
+        x1 = dequant_gemm(x, self.shared_w1_wq, self.shared_w1_scales, self.shared_w1_zeros, b, g)
+        x3 = dequant_gemm(x, self.shared_w3_wq, self.shared_w3_scales, self.shared_w3_zeros, b, g)
+        return dequant_gemm(F.silu(x1) * x3, self.shared_w2_wq, self.shared_w2_scales, self.shared_w2_zeros, b, g)
+
+    def forward_n_tokens(self, hidden_states: Tensor) -> Tensor:
+        """gemq/inference/moe_block.py:448-486.  A handful of rows (decode batches) run the
+        fused one-token kernels row by row with this path's fp32 routing."""
+        b, s, d = hidden_states.shape
+        x = hidden_states.reshape(-1, d)
+        if x.shape[0] <= _MAX_LOOPED_TOKENS:
+            xh = x if x.dtype == torch.float16 else x.to(torch.float16)
+            out, _, _ = self._decode(xh.contiguous(), ROUTE_FP32)
+            return out.to(hidden_states.dtype).reshape(b, s, d)
+        rw, sel, _ = self._route(x, ROUTE_FP32, bool(self.norm_topk_prob))
+        out = self._experts_n_tokens(x, rw, sel)
+        xh = x if x.dtype == torch.float16 else x.to(torch.float16)
+        out = out + self._shared_ffn(xh).to(x.dtype)
+        return out.reshape(b, s, d)
+
+    def forward_one_token(self, hidden_states: Tensor) -> Tensor:
+        """gemq/inference/moe_block.py:488-531."""
+        b, s, d = hidden_states.shape
+        x = hidden_states.reshape(-1, self.hidden_dim)
+        assert x.shape[0] == 1, f"Only supports single token forward. Got {x.shape[0]} tokens."
+        xh = x if x.dtype == torch.float16 else x.to(torch.float16)
+        out, _, _ = self._decode(xh.contiguous(), ROUTE_FP32)
+        return out.to(hidden_states.dtype).reshape(b, s, d)
+
+    def forward(self, hidden_states: Tensor) -> Tensor:
+        if hidden_states.shape[0] == hidden_states.shape[1] == 1:
+            return self.forward_one_token(hidden_states)
+        return self.forward_n_tokens(hidden_states)

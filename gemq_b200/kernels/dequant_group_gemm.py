@@ -1,0 +1,69 @@
+"""Grouped dequant GEMM over selected experts; same call signature as
+gemq/triton_kernels/dequant_group_gemm.py."""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from .. import _capi
+from ._runtime import gemv_workspace, require, require_cuda, stream_ptr
+
+_ROW_BLOCK = 64
+_group_size_cache: dict = {}
+
+
+def _uniform_group_size(group_sizes: Tensor) -> int:
+    """The block-wide group size (gemq/inference/moe_block.py:130-134 asserts it is uniform).
+    Read from the device once per tensor."""
+    key = (group_sizes.data_ptr(), group_sizes.numel())
+    g = _group_size_cache.get(key)
+    if g is None:
+        vals = torch.unique(group_sizes).tolist()
+        require(len(vals) == 1, "Group sizes must be the same across all experts.")
+        g = int(vals[0])
+        _group_size_cache[key] = g
+    return g
+
+
+def dequant_group_gemm(x: Tensor, indices: Tensor, wq: Tensor, scales: Tensor, zeros: Tensor,
+                       nbits: Tensor, group_sizes: Tensor, wq_strides: Tensor, zs_strides: Tensor,
+                       compute_dtype=torch.float16) -> Tensor:
+    """``output[g] = x @ dequantize(W[indices[g]])`` -> ``[A, M, N]``
+    (gemq/triton_kernels/dequant_group_gemm.py:155-202)."""
+    dev = require_cuda(x, indices, wq, scales, zeros, nbits, group_sizes, wq_strides, zs_strides)
+    require(compute_dtype == torch.float16, "only float16 is supported, as in the reference kernel")
+    require(x.dim() == 2 and x.dtype == torch.float16, "x must be float16 [M, K]")
+    require(indices.dtype == torch.int64, "indices must be int64")
+    indices = indices.reshape(-1)
+    require(wq.dtype == torch.int32 and wq.is_contiguous(), "wq must be contiguous int32")
+    require(scales.dtype == torch.float16 and zeros.dtype == torch.float16, "scales / zeros must be float16")
+    for t in (nbits, group_sizes, wq_strides, zs_strides):
+        require(t.dtype == torch.int32, "metadata tensors must be int32")
+    G = _uniform_group_size(group_sizes)
+    M, K = x.shape
+    N = wq.shape[1]
+    A = indices.shape[0]
+    x = x if x.stride(1) == 1 else x.contiguous()
+    scales = scales.contiguous()
+    zeros = zeros.contiguous()
+    out = torch.empty((A, M, N), dtype=torch.float16, device=dev)
+    if M <= _ROW_BLOCK:
+        blocks = [(0, M, out)]
+    else:
+        blocks = []
+        for i in range(0, M, _ROW_BLOCK):
+            m = min(_ROW_BLOCK, M - i)
+            blocks.append((i, m, torch.empty((A, m, N), dtype=torch.float16, device=dev)))
+    for i, m, dst in blocks:
+        ws = gemv_workspace(dev, A * N, K, m)
+        xs = x[i:i + m]
+        _capi.check("gemq_dequant_group_gemv", _capi.lib.gemq_dequant_group_gemv(
+            xs.data_ptr(), xs.stride(0), indices.data_ptr(), A, wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+            nbits.data_ptr(), wq_strides.data_ptr(), zs_strides.data_ptr(), dst.data_ptr(), m, N, K, G,
+            ws.data_ptr(), ws.numel(), stream_ptr(dev)))
+        if dst is not out:
+            out[:, i:i + m] = dst
+    return out
+
+
+dequant_group_gemm_triton = dequant_group_gemm

@@ -1,0 +1,75 @@
+"""Seeded synthetic weights and inputs with the shapes and value distributions of the
+benchmark configurations (there are no checkpoints or datasets in the build environment).
+
+Codes are uniform in ``[0, 2^b)``, the per-group fp16 scale is ``|N(0,1)| * 0.01 + 1e-3`` and
+the fp16 zero-point is uniform in ``[0, 2^b - 1]``; the kernels receive the additive offset
+``-zero * scale``.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import torch
+
+from .inference.moe_block import QuantFusedDeepseekV2MoEBlock, QuantFusedMixtralMoEBlock
+from .inference.packed_linear import PackedLinear
+
+MIXTRAL_8X7B = dict(hidden_size=4096, intermediate_size=14336, num_local_experts=8, num_experts_per_tok=2)
+DEEPSEEK_V2_LITE = dict(hidden_size=2048, moe_intermediate_size=1408, n_routed_experts=64, n_shared_experts=2,
+                        num_experts_per_tok=6, norm_topk_prob=False)
+
+
+def generator(seed: int, device) -> torch.Generator:
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return g
+
+
+def draw_codes_meta(out_f: int, in_f: int, nbits: int, group: int, gen: torch.Generator, device):
+    """codes uint8 [out, in], scale fp16 [in/group, out], zero-point fp16 [in/group, out]."""
+    codes = torch.randint(0, 2 ** nbits, (out_f, in_f), dtype=torch.uint8, device=device, generator=gen)
+    scale = (torch.randn(in_f // group, out_f, device=device, generator=gen).abs() * 0.01 + 1e-3).to(torch.float16)
+    zero = (torch.rand(in_f // group, out_f, device=device, generator=gen) * (2 ** nbits - 1)).to(torch.float16)
+    return codes, scale, zero
+
+
+def make_linear(out_f: int, in_f: int, nbits: int, group: int, gen: torch.Generator, device) -> PackedLinear:
+    codes, scale, zero = draw_codes_meta(out_f, in_f, nbits, group, gen, device)
+    return PackedLinear.from_codes(codes, scale, zero, nbits, group)
+
+
+def draw_expert_bits(n_experts: int, seed: int, lo: float = 1.5, hi: float = 2.5):
+    """Per-expert bit-widths from {1,2,3,4} whose mean lies in [lo, hi]."""
+    g = torch.Generator().manual_seed(seed)
+    while True:
+        bits = torch.randint(1, 5, (n_experts,), generator=g).tolist()
+        if lo <= sum(bits) / n_experts <= hi:
+            return bits
+
+
+def mixtral_block(seed: int = 0, device="cuda", bits=None, group: int = 128, **overrides) -> QuantFusedMixtralMoEBlock:
+    cfg = SimpleNamespace(**{**MIXTRAL_8X7B, **overrides})
+    E, D, Fd = cfg.num_local_experts, cfg.hidden_size, cfg.intermediate_size
+    bits = bits or draw_expert_bits(E, seed)
+    gen = generator(seed, device)
+    gate = (torch.randn(E, D, device=device, generator=gen) * 0.02).to(torch.float16)
+    w1 = [make_linear(Fd, D, b, group, gen, device) for b in bits]
+    w3 = [make_linear(Fd, D, b, group, gen, device) for b in bits]
+    w2 = [make_linear(D, Fd, b, group, gen, device) for b in bits]
+    return QuantFusedMixtralMoEBlock.from_linears(cfg, gate, w1, w2, w3)
+
+
+def deepseek_block(seed: int = 0, device="cuda", bits=None, shared_bits: int = 4, group: int = 128,
+                   **overrides) -> QuantFusedDeepseekV2MoEBlock:
+    cfg = SimpleNamespace(**{**DEEPSEEK_V2_LITE, **overrides})
+    E, D, Fd = cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size
+    SF = cfg.n_shared_experts * Fd
+    bits = bits or draw_expert_bits(E, seed)
+    gen = generator(seed, device)
+    gate = (torch.randn(E, D, device=device, generator=gen) / D ** 0.5).to(torch.float16)  # logits ~ N(0, 1)
+    w1 = [make_linear(Fd, D, b, group, gen, device) for b in bits]
+    w3 = [make_linear(Fd, D, b, group, gen, device) for b in bits]
+    w2 = [make_linear(D, Fd, b, group, gen, device) for b in bits]
+    shared = (make_linear(SF, D, shared_bits, group, gen, device), make_linear(D, SF, shared_bits, group, gen, device),
+              make_linear(SF, D, shared_bits, group, gen, device))
+    return QuantFusedDeepseekV2MoEBlock.from_linears(cfg, gate, w1, w2, w3, shared)

@@ -1,0 +1,181 @@
+/*
+ * gemq_b200 -- C ABI of the B200 (sm_100a) kernels for GEMQ's real-quantized MoE
+ * inference path.
+ *
+ * Every entry point takes raw device pointers and explicit extents, launches on
+ * the given stream, never allocates, never synchronises and returns 0 or a
+ * negative GEMQ_ERR_* code.  "Kernel form" tensors are the ones the reference's
+ * kernels consume:
+ *   wq      int32 [ceil(K/eps), N] contiguous, eps = 32 / nbits, code k of column n
+ *           in word (k / eps, n) at bit (k % eps) * nbits
+ *           (gemq/triton_kernels/utils.py:47-70, gemq/inference/moe_block.py:111-119)
+ *   scales, zeros  fp16 [K/G, N];  W^T[k,n] = fp16(fma(fp16(q), scales, zeros))
+ *           (gemq/triton_kernels/utils.py:206-210)
+ *   stacked experts: tensors concatenated along dim 0, nbits[E] int32, wq_strides[E] /
+ *           zs_strides[E] int32 element offsets (gemq/inference/moe_block.py:122-142)
+ * Expert indices are int64 device tensors as produced by torch.topk
+ * (gemq/inference/moe_block.py:213).
+ */
+#ifndef GEMQ_B200_H_
+#define GEMQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* gemq_stream_t; /* cudaStream_t */
+
+enum {
+  GEMQ_OK = 0,
+  GEMQ_ERR_BAD_ARG = -1,     /* null pointer, non-positive extent, unsupported bit-width */
+  GEMQ_ERR_BAD_SHAPE = -2,   /* extents the kernels cannot take (see each function) */
+  GEMQ_ERR_WORKSPACE = -3,   /* workspace missing or too small */
+  GEMQ_ERR_LAUNCH = -4,      /* CUDA reported a launch error */
+  GEMQ_ERR_ALIGN = -5        /* a pointer is not 16-byte aligned */
+};
+
+/* Library identification; returns a static string. */
+const char* gemq_version(void);
+
+/* Bytes of zero-initialised device workspace the GEMV-family calls need for the
+ * given problem: fp32 split-K partials plus arrival counters.  The counters are
+ * left at zero by every call, so one memset at allocation time is enough.
+ * `total_cols` = columns summed over all (slot, matrix) jobs of a launch,
+ * `max_k` = largest reduction length, `tokens` = activation rows. */
+size_t gemq_gemv_workspace_bytes(int total_cols, int max_k, int tokens);
+
+/* ---- packing format (gemq/triton_kernels/utils.py) ---------------------------- */
+
+/* pack_weights_over_cols_triton, transpose=False form (utils.py:74-113):
+ * codes uint8 [rows, cols] -> int32 [rows, ceil(cols/eps)], tail lanes zero. */
+int gemq_pack_over_cols(const uint8_t* codes, int32_t* packed, int rows, int cols, int nbits,
+                        gemq_stream_t stream);
+
+/* Kernel-form pack: codes uint8 [N, K] -> int32 [ceil(K/eps), N] contiguous, i.e.
+ * pack(..., transpose=True).contiguous() (utils.py:110-111, moe_block.py:111-119). */
+int gemq_pack_kernel_form(const uint8_t* codes, int32_t* wq, int N, int K, int nbits, gemq_stream_t stream);
+
+/* unpack_over_cols_triton (utils.py:149-189): int32 [rows, words] -> uint8 [rows, out_cols]. */
+int gemq_unpack_over_cols(const int32_t* packed, uint8_t* codes, int rows, int words, int out_cols,
+                          int nbits, gemq_stream_t stream);
+
+/* dequantize (utils.py:192-212) materialised: kernel-form -> fp16 W^T [K, N], bit-exact
+ * single-rounded fp16 fma. */
+int gemq_dequantize(const int32_t* wq, const void* scales, const void* zeros, void* out_kn,
+                    int K, int N, int nbits, int group_size, gemq_stream_t stream);
+
+/* ---- decode GEMV family ---------------------------------------------------------- */
+
+/* dequant_splitk_gemv_triton (gemq/triton_kernels/dequant_gemv.py:118-156), extended to
+ * `tokens` activation rows: y[t, :] = x[t, :] @ deq(wq).  x fp16 [tokens, K] (row stride
+ * ldx), y fp16 [tokens, N] (row stride ldy).  Deterministic (fixed-order split-K). */
+int gemq_dequant_gemv(const void* x, int ldx, const int32_t* wq, const void* scales, const void* zeros,
+                      void* y, int ldy, int tokens, int N, int K, int nbits, int group_size,
+                      void* workspace, size_t workspace_bytes, gemq_stream_t stream);
+
+/* dequant_sel_splitk_gemv_triton (dequant_gemv.py:225-270): expert idx[0] of stacked tensors. */
+int gemq_dequant_sel_gemv(const void* x, const int64_t* idx, const int32_t* wq, const void* scales,
+                          const void* zeros, const int32_t* nbits, const int32_t* wq_strides,
+                          void* y, int N, int K, int group_size,
+                          void* workspace, size_t workspace_bytes, gemq_stream_t stream);
+
+/* fused_dequant_up_proj_triton (gemq/triton_kernels/fused_dequant_bmm.py:122-173):
+ * x1[a*N+n], x3[a*N+n] = x @ deq(w1[idx[a]]), x @ deq(w3[idx[a]]); w1/w3 share nbits and
+ * w_strides (:56-57). */
+int gemq_fused_up_proj(const void* x, const int64_t* idx, int A,
+                       const int32_t* w1, const int32_t* w3,
+                       const void* w1_scales, const void* w1_zeros,
+                       const void* w3_scales, const void* w3_zeros,
+                       const int32_t* nbits, const int32_t* w_strides,
+                       void* x1, void* x3, int N, int K, int group_size,
+                       void* workspace, size_t workspace_bytes, gemq_stream_t stream);
+
+/* fused_dequant_down_proj_triton (fused_dequant_bmm.py:264-312):
+ * x2[a*N+n] = (silu(x1[a*K+k]) * x3[a*K+k]) @ deq(w2[idx[a]]). */
+int gemq_fused_down_proj(const void* x1, const void* x3, const int64_t* idx, int A,
+                         const int32_t* w2, const void* w2_scales, const void* w2_zeros,
+                         const int32_t* nbits, const int32_t* w_strides,
+                         void* x2, int N, int K, int group_size,
+                         void* workspace, size_t workspace_bytes, gemq_stream_t stream);
+
+/* dequant_group_gemm_triton (gemq/triton_kernels/dequant_group_gemm.py:155-202) for a small
+ * number of rows: y[g, t, :] = x[t, :] @ deq(W[indices[g]]), x fp16 [tokens, K] (row stride
+ * ldx), y fp16 [A, tokens, N] contiguous.  Per-expert scale offsets come from zs_strides
+ * (:75,80-81); one group size for all experts. */
+int gemq_dequant_group_gemv(const void* x, int ldx, const int64_t* indices, int A,
+                            const int32_t* wq, const void* scales, const void* zeros,
+                            const int32_t* nbits, const int32_t* wq_strides, const int32_t* zs_strides,
+                            void* y, int tokens, int N, int K, int group_size,
+                            void* workspace, size_t workspace_bytes, gemq_stream_t stream);
+
+/* ---- routing ------------------------------------------------------------------------ */
+
+/* Router: logits = x @ gate^T, softmax, top-k, optional renormalisation.
+ * mode 0: everything rounded through fp16 like the Mixtral one-token path
+ *         (gemq/inference/moe_block.py:211-214);
+ * mode 1: fp16-rounded logits, fp32 softmax (Mixtral n-token, :174-180);
+ * mode 2: fp32 logits and softmax (DeepSeek-V2, :457-464, :499-505).
+ * x [tokens, D] fp16 or bf16 (x_is_bf16), gate fp16/bf16 [E, D] in the same dtype.
+ * Outputs: idx int64 [tokens, A], weights [tokens, A] in the activation dtype,
+ * logits fp32 [tokens, E] (may be NULL). */
+int gemq_moe_route(const void* x, const void* gate, int tokens, int D, int E, int A,
+                   int mode, int renorm, int x_is_bf16,
+                   int64_t* idx, void* weights, float* logits, gemq_stream_t stream);
+
+/* ---- whole decode layer --------------------------------------------------------------- */
+
+/* One stacked projection family of a layer (all pointers device memory). */
+typedef struct {
+  const int32_t* wq;
+  const void* scales;
+  const void* zeros;
+  const int32_t* nbits;      /* [E] */
+  const int32_t* wq_strides; /* [E] */
+  const int32_t* zs_strides; /* [E] or NULL: expert e starts at row e*(K/G) */
+} gemq_stacked_t;
+
+/* One single (non-stacked) quantised matrix, e.g. a DeepSeek-V2 shared-expert projection. */
+typedef struct {
+  const int32_t* wq;
+  const void* scales;
+  const void* zeros;
+  int nbits;
+  int group_size;
+} gemq_single_t;
+
+typedef struct {
+  int hidden;        /* D */
+  int ffn;           /* F */
+  int n_experts;     /* E */
+  int top_k;         /* A */
+  int group_size;    /* block_group_size (moe_block.py:130-134) */
+  int route_mode;    /* see gemq_moe_route */
+  int renorm;        /* norm_topk_prob */
+  int shared_ffn;    /* 0, or n_shared * F (moe_block.py:400-412) */
+  const void* gate;  /* fp16 [E, D] */
+  gemq_stacked_t w1, w3, w2;
+  gemq_single_t s1, s3, s2; /* used when shared_ffn > 0 */
+} gemq_moe_layer_t;
+
+/* Device scratch of one decode step; sizes from gemq_moe_decode_scratch_bytes. */
+size_t gemq_moe_decode_scratch_bytes(const gemq_moe_layer_t* layer);
+
+/* forward_one_token of QuantFusedMixtralMoEBlock / QuantFusedDeepseekV2MoEBlock
+ * (gemq/inference/moe_block.py:200-235, :488-531) applied to `tokens` rows one after the
+ * other: route (all rows in one launch), then per row the fused gate/up projection and
+ * SiLU*mul + down projection whose epilogue does the top-k weighted combine (+ shared
+ * experts).  x, out: fp16 [tokens, D].  idx int64 [tokens, A] and w fp16 [tokens, A] hold the
+ * routing: written when do_route != 0 (route_mode as in gemq_moe_route, normally
+ * layer->route_mode), read when do_route == 0.  `scratch` must have been zero-filled once
+ * before its first use; calls sharing it must be ordered on one stream. */
+int gemq_moe_decode(const gemq_moe_layer_t* layer, const void* x, void* out,
+                    int64_t* idx, void* w, int tokens, int do_route, int route_mode,
+                    void* scratch, size_t scratch_bytes, gemq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEMQ_B200_H_ */

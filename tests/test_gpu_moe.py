@@ -1,0 +1,121 @@
+"""Layer-level parity of the quantised MoE blocks with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gemq_oracle as O
+from conftest import MAX_ABS_TOL, REL_FRO_TOL, max_abs, rel_fro
+import moe_fixtures as MF
+
+pytestmark = pytest.mark.gpu
+
+
+def check(got, want):
+    got = got.float().cpu().numpy()
+    want = np.asarray(want, dtype=np.float32)
+    assert rel_fro(got, want) < REL_FRO_TOL, f"rel-Frobenius {rel_fro(got, want):.3e}"
+    assert max_abs(got, want) < MAX_ABS_TOL, f"max-abs {max_abs(got, want):.3e}"
+
+
+def clear_margin(logits, k, eps=2e-2):
+    v = np.sort(np.asarray(logits, dtype=np.float64).ravel())[::-1]
+    return (v[k - 1] - v[k]) > eps * max(1.0, abs(v[k - 1]))
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_mixtral_one_token_small(seed):
+    layer = MF.make_layer("mixtral", D=256, Fd=512, E=4, A=2, bits=[1, 2, 3, 4], seed=seed, gate_std=0.02)
+    blk = MF.gpu_block(layer)
+    w1, w3, w2, _ = MF.oracle_parts(layer)
+    x = torch.randn(1, 256, generator=torch.Generator().manual_seed(seed)).half()
+    out, aux = blk(x.cuda().view(1, 1, -1))
+    assert aux is None and out.shape == (1, 1, 256) and out.dtype == torch.float16
+    _, gw, gi = blk._decode(x.cuda(), 0)
+    ref_out, ew, ei = O.moe_one_token(x, torch.from_numpy(layer["gate"]), 2, w1, w3, w2, "mixtral")
+    # against fp32-accumulated math with the routing the GPU chose
+    check(out.view(1, -1), O.moe_reference_fp32(x, gw.float().cpu(), gi.cpu(), w1, w3, w2))
+    scores = (x.float() @ torch.from_numpy(layer["gate"]).float().t()).numpy()
+    if clear_margin(scores, 2):
+        assert sorted(gi.cpu().view(-1).tolist()) == sorted(ei.view(-1).tolist())
+        check(out.view(1, -1), ref_out.float().numpy())
+        order = np.argsort(gi.cpu().view(-1).numpy()), np.argsort(ei.view(-1).numpy())
+        assert np.allclose(gw.float().cpu().view(-1).numpy()[order[0]], ew.float().view(-1).numpy()[order[1]], atol=2e-3)
+
+
+@pytest.mark.parametrize("norm", [False, True])
+def test_deepseek_one_token_small(norm):
+    layer = MF.make_layer("deepseek", D=256, Fd=384, E=16, A=6, bits=[1, 2, 3, 4] * 4, seed=3, gate_std=1 / 16.0,
+                          n_shared=2, shared_bits=4, norm_topk_prob=norm)
+    blk = MF.gpu_block(layer)
+    w1, w3, w2, sh = MF.oracle_parts(layer)
+    x = torch.randn(1, 256, generator=torch.Generator().manual_seed(9)).half()
+    out = blk(x.cuda().view(1, 1, -1))
+    assert isinstance(out, torch.Tensor) and out.shape == (1, 1, 256)
+    _, gw, gi = blk._decode(x.cuda(), 2)
+    check(out.view(1, -1), O.moe_reference_fp32(x, gw.float().cpu(), gi.cpu(), w1, w3, w2, sh))
+    ref_out, ew, ei = O.moe_one_token(x, torch.from_numpy(layer["gate"]), 6, w1, w3, w2, "deepseek", norm, sh)
+    logits = (x.float() @ torch.from_numpy(layer["gate"]).float().t()).numpy()
+    if clear_margin(logits, 6):
+        assert sorted(gi.cpu().view(-1).tolist()) == sorted(ei.view(-1).tolist())
+        check(out.view(1, -1), ref_out.float().numpy())
+
+
+def test_deepseek_decode_batch_rows():
+    """[B, 1, D] decode batches take the n-token path of the reference (fp32 routing)."""
+    layer = MF.make_layer("deepseek", D=256, Fd=384, E=16, A=6, bits=[1, 2, 3, 4] * 4, seed=4, gate_std=1 / 16.0,
+                          n_shared=2)
+    blk = MF.gpu_block(layer)
+    w1, w3, w2, sh = MF.oracle_parts(layer)
+    x = torch.randn(5, 256, generator=torch.Generator().manual_seed(1)).half()
+    out = blk(x.cuda().view(5, 1, -1)).view(5, -1)
+    _, gw, gi = blk._decode(x.cuda(), 2)
+    check(out, O.moe_reference_fp32(x, gw.float().cpu(), gi.cpu(), w1, w3, w2, sh))
+
+
+def test_mixtral_n_tokens_small():
+    layer = MF.make_layer("mixtral", D=256, Fd=512, E=4, A=2, bits=[4, 1, 3, 2], seed=5, gate_std=0.02)
+    blk = MF.gpu_block(layer)
+    w1, w3, w2, _ = MF.oracle_parts(layer)
+    x = torch.randn(37, 256, generator=torch.Generator().manual_seed(2)).half()
+    out, logits = blk(x.cuda().view(1, 37, -1))
+    assert logits.shape == (37, 4)
+    rw, sel, _ = blk._route(x.cuda(), 1, True)
+    ref_out, ew, ei, ref_logits = O.moe_n_tokens(x, torch.from_numpy(layer["gate"]), 2, w1, w3, w2, "mixtral")
+    assert np.allclose(logits.float().cpu().numpy(), ref_logits.float().numpy(), atol=2e-3)
+    same = (sel.cpu().sort(dim=1).values == ei.sort(dim=1).values).all(dim=1)
+    assert same.float().mean() > 0.9
+    got = out.view(37, -1).float().cpu()[same]
+    check(got, ref_out.float()[same].numpy())
+
+
+def test_mixtral_config1_full_size_decode():
+    """Mixtral-8x7B-shaped layer, decode batch 1, mixed bits with mean in [1.5, 2.5]."""
+    from gemq_b200 import synth
+    blk = synth.mixtral_block(seed=0)
+    x = torch.randn(1, 1, 4096, generator=torch.Generator().manual_seed(0)).half().cuda()
+    out, _ = blk(x)
+    _, gw, gi = blk._decode(x.view(1, -1), 0)
+    # oracle on the two selected experts only, from the block's own packed tensors
+    sel = gi.view(-1).tolist()
+    D, Fd, G = 4096, 14336, 128
+    acc = np.zeros(D, dtype=np.float64)
+    xf = x.view(1, -1).float().cpu().numpy()
+    for a, e in enumerate(sel):
+        b = blk._nbits_host[e]
+
+        def mat(name, K, N):
+            off = int(getattr(blk, f"{name}_wq_strides")[e])
+            rows = -(-K // (32 // b))
+            wq = getattr(blk, f"{name}_wq").view(-1)[off:off + rows * N].view(rows, N).cpu().numpy()
+            zo = int(getattr(blk, f"{name}_zs_strides")[e])
+            s = getattr(blk, f"{name}_scales").view(-1)[zo:zo + (K // G) * N].view(K // G, N).cpu().numpy()
+            z = getattr(blk, f"{name}_zeros").view(-1)[zo:zo + (K // G) * N].view(K // G, N).cpu().numpy()
+            return O.dequantize(wq, s, z, b, G, K).astype(np.float32)
+
+        h1 = xf @ mat("w1", D, Fd)
+        h3 = xf @ mat("w3", D, Fd)
+        h = (h1 / (1 + np.exp(-h1))) * h3
+        acc += float(gw.view(-1)[a]) * (h @ mat("w2", Fd, D))[0]
+    check(out.view(1, -1), acc[None, :])
+    out2, _ = blk(x)
+    assert torch.equal(out, out2)
