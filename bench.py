@@ -36,6 +36,8 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=8)
     p.add_argument("--cpu-sample-cols", type=int, default=1792)
+    p.add_argument("--mode", default="bench", choices=["bench", "up_only", "layer_only"],
+                   help="up_only / layer_only: a short eager loop of one op for profilers; prints its own timing")
     return p.parse_args()
 
 
@@ -149,6 +151,35 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+def profile_loop(args, blocks, xs, pairs, dev):
+    """Eager launches of one op (no graphs), for ncu: warmup + steps iterations."""
+    import torch
+    from gemq_b200.kernels import fused_dequant_up_proj
+    routed = [blocks[li]._decode(xs[xi].view(1, D), 0)[2][0].clone() for li, xi in pairs]
+
+    def once(i):
+        li, xi = pairs[i % len(pairs)]
+        b = blocks[li]
+        if args.mode == "up_only":
+            fused_dequant_up_proj(xs[xi].view(1, D), routed[i % len(pairs)], b.w1_wq, b.w3_wq, b.w1_scales,
+                                  b.w1_zeros, b.w3_scales, b.w3_zeros, b.w1_nbits, b.w1_wq_strides, G)
+        else:
+            b(xs[xi])
+
+    for i in range(args.warmup):
+        once(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        once(i)
+    e1.record()
+    torch.cuda.synchronize()
+    bits = [[blocks[li]._nbits_host[e] for e in r.tolist()] for (li, _), r in zip(pairs, routed)]
+    print(json.dumps({"mode": args.mode, "steps": args.steps, "avg_us": e0.elapsed_time(e1) * 1e3 / args.steps,
+                      "bits_of_selected_experts": bits[:args.steps + args.warmup]}))
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -177,8 +208,12 @@ def main():
     xs = torch.randn(n_x, 1, 1, D, device=dev, generator=gen).to(torch.float16)
     torch.cuda.synchronize()
 
-    # ---- device-resident throughput: one CUDA graph per (layer, activation) pair --------------
     pairs = [(i % L, i % n_x) for i in range(max(L, 16))]
+    if args.mode != "bench":
+        profile_loop(args, blocks, xs, pairs, dev)
+        return
+
+    # ---- device-resident throughput: one CUDA graph per (layer, activation) pair --------------
     graphs = []
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
