@@ -517,7 +517,11 @@ __global__ void __launch_bounds__(kCtaThreads) gemv_mma_kernel(const __grid_cons
     for (int tc = 0; tc < nt; ++tc) {
       const float* src = P.partial + static_cast<size_t>(t0 + tc) * P.c_total + J.col_base + n;
       float sum = 0.f;
-      for (int s = 0; s < R.slices; ++s) sum += ld_cg_f32(src + static_cast<size_t>(s) * P.T * P.c_total);
+      for (int s = 0; s < R.slices; ++s) {
+        float* q = const_cast<float*>(src) + static_cast<size_t>(s) * P.T * P.c_total;
+        sum += ld_cg_f32(q);
+        __stcg(q, 0.f);  // the partial region is all-zero between launches (the persistent kernel relies on it)
+      }
       J.y[static_cast<size_t>(t0 + tc) * J.ldy + n] = __float2half_rn(sum);
     }
   } else {
@@ -528,7 +532,11 @@ __global__ void __launch_bounds__(kCtaThreads) gemv_mma_kernel(const __grid_cons
       const int sl = resolve_job(Ji, kGroup).slices;
       const float* src = P.partial + Ji.col_base + n;
       float sum = 0.f;
-      for (int s = 0; s < sl; ++s) sum += ld_cg_f32(src + static_cast<size_t>(s) * P.T * P.c_total);
+      for (int s = 0; s < sl; ++s) {
+        float* q = const_cast<float*>(src) + static_cast<size_t>(s) * P.T * P.c_total;
+        sum += ld_cg_f32(q);
+        __stcg(q, 0.f);
+      }
       const __half x2 = __float2half_rn(sum);
       if (Ji.y) Ji.y[n] = x2;
       if (i < P.comb_weighted) {
@@ -594,9 +602,12 @@ struct Workspace {
 };
 
 size_t gemv_workspace_bytes(int total_cols, int max_k, int tokens) {
-  const size_t s_max = static_cast<size_t>(cdiv(cdiv(max_k, kGroup), kSliceGroups));
+  // the persistent kernel cuts 4-bit matrices into 4-group slices, the shortest of all
+  const size_t s_max = static_cast<size_t>(cdiv(cdiv(max_k, kGroup), 4));
+  // counters | fp32 partial slots | fp32 activation staging of the SiLU*mul inputs (one row per job)
   return static_cast<size_t>(kMaxCounters) * sizeof(int) +
-         s_max * static_cast<size_t>(tokens) * static_cast<size_t>(total_cols) * sizeof(float);
+         s_max * static_cast<size_t>(tokens) * static_cast<size_t>(total_cols) * sizeof(float) +
+         static_cast<size_t>(kMaxJobs) * static_cast<size_t>(max_k) * sizeof(float);
 }
 
 static bool split_ws(void* ws, size_t bytes, Workspace* out) {
@@ -632,7 +643,7 @@ static int launch_mma(GemvParams& P, const Workspace& W, cudaStream_t stream) {
   P.G = kGroup;
   const int tt = P.T <= 1 ? 1 : (P.T <= 2 ? 2 : (P.T <= 4 ? 4 : 8));
   const int tblocks = cdiv(P.T, tt);
-  if (static_cast<size_t>(chunks) * tblocks > static_cast<size_t>(kMaxCounters)) return GEMQ_ERR_WORKSPACE;
+  if (static_cast<size_t>(chunks) * tblocks >= static_cast<size_t>(kMaxCounters - 1)) return GEMQ_ERR_WORKSPACE;
   if (static_cast<size_t>(P.s_max) * P.T * cols > W.partial_floats) return GEMQ_ERR_WORKSPACE;
   if (tblocks > 65535) return GEMQ_ERR_BAD_SHAPE;
   P.partial = W.partial;
@@ -667,6 +678,28 @@ int run_gemv_jobs(GemvParams& P, bool silu, int G, void* workspace, size_t works
   if (fast) {
     Workspace W;
     if (!split_ws(workspace, workspace_bytes, &W)) return GEMQ_ERR_WORKSPACE;
+    bool act_aligned = true;
+    for (int i = 0; i < P.n_jobs; ++i) act_aligned = act_aligned && aligned16(P.jobs[i].xa) && aligned16(P.jobs[i].xb);
+    if (P.T == 1 && act_aligned) {
+      if (silu) {
+        // stage h = silu(x1) * x3 in fp32 at the tail of the workspace, one row per job
+        int max_k = 0;
+        for (int i = 0; i < P.n_jobs; ++i) max_k = P.jobs[i].K > max_k ? P.jobs[i].K : max_k;
+        const size_t hfloats = static_cast<size_t>(P.n_jobs) * max_k;
+        if (W.partial_floats < hfloats) return GEMQ_ERR_WORKSPACE;
+        W.partial_floats -= hfloats;
+        float* h = W.partial + W.partial_floats;
+        for (int i = 0; i < P.n_jobs; ++i) {
+          GemvJob& J = P.jobs[i];
+          float* hi = h + static_cast<size_t>(i) * max_k;
+          if (int rc = silu_mul_f32(J.xa, J.xb, hi, J.K, stream)) return rc;
+          J.xa = reinterpret_cast<const __half*>(hi);
+          J.xb = nullptr;
+        }
+        P.x_f32 = 1;
+      }
+      return launch_stream(P, W.partial, W.partial_floats, W.counters, stream);
+    }
     return silu ? launch_mma<true>(P, W, stream) : launch_mma<false>(P, W, stream);
   }
   if (P.comb_out) return GEMQ_ERR_BAD_SHAPE;
@@ -755,6 +788,7 @@ extern "C" int gemq_fused_up_proj(const void* x, const int64_t* idx, int A,
       J.N = N; J.K = K; J.ldx = K; J.ldy = A * N;
     }
   }
+  P.epi = kEpiUpPair;
   return run_gemv_jobs(P, false, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 

@@ -34,12 +34,19 @@ struct GemvJob {
   const __half* xa;        // activation rows [T, K]; with SILU: x1 of this slot
   const __half* xb;        // with SILU: x3 of this slot
   __half* y;               // output rows [T, N] (may be nullptr in combine mode)
+  float* h;                // up-pair epilogue: fp32 silu(x1)*x3 of this slot (first job of a pair), or nullptr
   int fixed_bits;
   int N, K;
   int ldx, ldy;
   int col_base;            // first column of this job inside a partial row
   int tile_base;           // first blockIdx.x of this job
-  int chunk_base;          // first arrival counter of this job
+  int chunk_base;          // first arrival counter of this job (shared by the jobs of a finish group)
+};
+
+// How a finished column chunk is turned into outputs (persistent kernel).
+enum { kEpiStore = 0,   // y = fp16(sum), each job on its own
+       kEpiUpPair = 1,  // jobs (2i, 2i+1) = gate/up projection of one slot: x1, x3 and h = silu(x1)*x3
+       kEpiCombine = 2  // all jobs: weighted top-k combine (+ unit-weight shared experts)
 };
 
 struct GemvParams {
@@ -58,6 +65,8 @@ struct GemvParams {
   __half* comb_out;
   const __half* comb_w;
   int comb_weighted;
+  int epi;         // kEpi* (persistent kernel)
+  int x_f32;       // activations are fp32 vectors (persistent kernel, e.g. h from the up-pair epilogue)
 };
 
 struct ResolvedJob {
@@ -88,5 +97,8 @@ __device__ __forceinline__ ResolvedJob resolve_job(const GemvJob& J, int G) {
 // otherwise).  Defined in gemv.cu.
 int run_gemv_jobs(GemvParams& P, bool silu, int G, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 size_t gemv_workspace_bytes(int total_cols, int max_k, int tokens);
+// Persistent bulk-copy kernel for one activation row (gemv_stream.cu).
+int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* counters, cudaStream_t stream);
+int silu_mul_f32(const __half* x1, const __half* x3, float* h, int n, cudaStream_t stream);
 
 }  // namespace gemq

@@ -1,0 +1,793 @@
+// Persistent, bulk-copy fed dequant GEMV for one activation row (decode batch 1).
+//
+// One CTA per SM.  The launch's work is cut into units of 64 packed word rows x 128
+// output columns of one job (32 KB of codes plus the group metadata: 2048 / 1024 / 640 /
+// 512 reduction elements at 1 / 2 / 3 / 4 bits).  Units are ordered job-major, column
+// chunk-major, k-slice-minor and dealt to the CTAs in contiguous, byte-balanced ranges, so
+// a CTA usually owns all slices of a chunk and keeps the running sums on chip.  Inside a
+// CTA four roles run concurrently:
+//   * a producer warp streams the units into a 4-stage shared-memory ring with
+//     cp.async.bulk (one 512-byte copy per word row, mbarrier transaction counts): about
+//     130 KB per SM are in flight whatever the other warps are doing;
+//   * a table warp turns the activation slice of each unit into the pre-scaled fp16
+//     operand table of that stage (one power-of-two scale and one sum per group);
+//   * sixteen consumer warps (4 column strips x 4 row quarters) run the in-place
+//     subnormal-fp16 mma.sync scheme described in gemv.cu on the staged words and
+//     accumulate over the consecutive slices of a chunk in registers;
+//   * a finisher warp adds the four row quarters in a fixed order and writes the result:
+//     directly when this CTA covered the whole reduction, otherwise through zero-restoring
+//     fp32 partial slots and an arrival counter (the warp that completes a chunk adds the
+//     slots in order and runs the epilogue).  Global-memory latency of this protocol never
+//     stalls the consumers.
+// Every wait is bounded: on expiry the kernel records an error code and keeps going.
+#include "gemv.cuh"
+
+namespace gemq {
+
+constexpr int kSConsumers = 16;
+constexpr int kWarpProducer = kSConsumers;
+constexpr int kWarpTable = kSConsumers + 1;
+constexpr int kWarpFinisher = kSConsumers + 2;
+constexpr int kSWarps = kSConsumers + 3;
+constexpr int kSThreads = 32 * kSWarps;
+constexpr int kSStages = 4;
+constexpr int kRedSlots = 4;
+constexpr int kUnitRows = 64;
+constexpr int kRowPitch = 544;  // 512 B of words + 32 B pad: conflict-free 128-bit reads across 4 rows
+constexpr int kMaxUnitGroups = 16;
+constexpr int kSpinLimit = 1 << 18;
+constexpr int kErrSlot = kMaxCounters - 1;  // last counter word holds the error code
+
+enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrRedFullWait = 3, kErrRedEmptyWait = 4 };
+
+struct StageBuf {
+  alignas(16) unsigned char words[kUnitRows * kRowPitch];
+  alignas(16) __half scales[kMaxUnitGroups][128];
+  alignas(16) __half zeros[kMaxUnitGroups][128];
+  alignas(16) uint32_t tab[1024];   // 1/2/4-bit: [64 rows][eps halves]; 3-bit: [2 variants][64 rows][16 halves]
+  float xsum[kMaxUnitGroups];       // sum of the activations of each group
+  float fin[kMaxUnitGroups];        // 2^(24 - c_g): undoes the subnormal and activation scaling of each group
+};
+
+struct JobInfo {
+  const uint32_t* wq;
+  const __half* scales;
+  const __half* zeros;
+  int bits, slices, nch, groups_per_unit, ngroups, kw;
+};
+
+struct Range {
+  int job, ulo, uhi;
+};
+
+struct StreamSmem {
+  StageBuf stage[kSStages];
+  alignas(16) float red[kRedSlots][4][128];
+  alignas(16) uint32_t zero_row[16];
+  alignas(8) unsigned long long full[kSStages], empty[kSStages], redfull[kRedSlots], redempty[kRedSlots];
+  JobInfo info[kMaxJobs];
+  Range ranges[kMaxJobs];
+  int n_ranges;
+};
+
+struct Unit {
+  int job, slice, chunk, bits;
+  int n0, ncols, g0, ng, wr0, nrows;
+};
+
+// A run of consecutive k-slices [sa, sb) of one column chunk of one job.
+struct Part {
+  int job, chunk, sa, sb;
+};
+
+// ---- mbarrier / bulk-copy primitives -------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls, records `code` and returns.
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, uint32_t parity, int* err, int code) {
+  for (int i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return;
+  atomicExch(err, code);
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void mma16816s(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- unit geometry and the per-CTA plan -------------------------------------------------
+__device__ __forceinline__ int unit_groups(int bits) { return bits == 3 ? 5 : 16 / bits; }
+
+__device__ __forceinline__ void make_unit(const GemvJob& J, const JobInfo& I, int job, int slice, int chunk, Unit& U) {
+  U.job = job; U.slice = slice; U.chunk = chunk; U.bits = I.bits;
+  U.n0 = chunk * 128;
+  U.ncols = min(128, J.N - U.n0);
+  U.g0 = slice * I.groups_per_unit;
+  U.ng = min(I.groups_per_unit, I.ngroups - U.g0);
+  U.wr0 = slice * kUnitRows;
+  U.nrows = I.bits == 3 ? min(kUnitRows, I.kw - U.wr0) : U.ng * (4 * I.bits);
+}
+
+// Walks this CTA's parts in order; identical in every role.
+struct PartWalk {
+  int r, u;
+  __device__ __forceinline__ void begin(const StreamSmem& S) {
+    r = 0;
+    u = S.n_ranges > 0 ? S.ranges[0].ulo : 0;
+  }
+  __device__ __forceinline__ bool next(const StreamSmem& S, Part& Pt) {
+    while (r < S.n_ranges && u >= S.ranges[r].uhi) {
+      ++r;
+      if (r < S.n_ranges) u = S.ranges[r].ulo;
+    }
+    if (r >= S.n_ranges) return false;
+    const Range& R = S.ranges[r];
+    const int sl = S.info[R.job].slices;
+    Pt.job = R.job;
+    Pt.chunk = u / sl;
+    Pt.sa = u - Pt.chunk * sl;
+    Pt.sb = min(sl, Pt.sa + (R.uhi - u));
+    u += Pt.sb - Pt.sa;
+    return true;
+  }
+};
+
+// Warp 0: one lane per job resolves the expert (two dependent global loads) and sizes the
+// job; a warp scan of the byte costs then gives this CTA its contiguous unit range per job.
+__device__ void make_plan(StreamSmem& S, const GemvParams& P) {
+  const int lane = threadIdx.x & 31;
+  unsigned n_units = 0, unit_cost = 1;
+  if (lane < P.n_jobs) {
+    const GemvJob& J = P.jobs[lane];
+    const ResolvedJob R = resolve_job(J, kGroup);
+    JobInfo I;
+    I.wq = R.wq; I.scales = R.scales; I.zeros = R.zeros;
+    I.bits = R.bits < 1 ? 1 : (R.bits > 4 ? 4 : R.bits);
+    I.groups_per_unit = unit_groups(I.bits);
+    I.ngroups = J.K / kGroup;
+    I.slices = cdiv(I.ngroups, I.groups_per_unit);
+    I.nch = cdiv(J.N, 128);
+    I.kw = cdiv(J.K, 32 / I.bits);
+    S.info[lane] = I;
+    Unit U;
+    make_unit(J, I, lane, I.slices - 1, 0, U);
+    const unsigned chunk_cost = (I.slices - 1) * (kUnitRows + I.groups_per_unit) + U.nrows + U.ng;  // x 512 B
+    unit_cost = max(1u, chunk_cost / I.slices);
+    n_units = static_cast<unsigned>(I.nch) * I.slices;
+  }
+  const unsigned w = n_units * unit_cost;
+  unsigned incl = w;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const unsigned total = __shfl_sync(0xffffffffu, incl, 31);
+  const unsigned prefix = incl - w;
+  const unsigned lo = static_cast<unsigned>(static_cast<unsigned long long>(total) * blockIdx.x / gridDim.x);
+  const unsigned hi = static_cast<unsigned>(static_cast<unsigned long long>(total) * (blockIdx.x + 1) / gridDim.x);
+  unsigned ulo = lo <= prefix ? 0u : (lo - prefix + unit_cost - 1) / unit_cost;
+  unsigned uhi = hi <= prefix ? 0u : (hi - prefix + unit_cost - 1) / unit_cost;
+  ulo = min(ulo, n_units);
+  uhi = min(uhi, n_units);
+  const bool have = uhi > ulo;
+  const unsigned ballot = __ballot_sync(0xffffffffu, have);
+  if (have) {
+    Range R;
+    R.job = lane; R.ulo = static_cast<int>(ulo); R.uhi = static_cast<int>(uhi);
+    S.ranges[__popc(ballot & ((1u << lane) - 1u))] = R;
+  }
+  if (lane == 0) S.n_ranges = __popc(ballot);
+}
+
+// ---- producer ---------------------------------------------------------------------------
+__device__ void producer_role(StreamSmem& S, const GemvParams& P, int* err) {
+  const int lane = threadIdx.x & 31;
+  PartWalk W;
+  W.begin(S);
+  Part Pt;
+  int it = 0;
+  while (W.next(S, Pt)) {
+    const GemvJob& J = P.jobs[Pt.job];
+    const JobInfo& I = S.info[Pt.job];
+    for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
+      Unit U;
+      make_unit(J, I, Pt.job, sl, Pt.chunk, U);
+      const int st = it % kSStages;
+      const uint32_t par = (it / kSStages) & 1;
+      StageBuf& B = S.stage[st];
+      mbar_wait(&S.empty[st], par ^ 1, err, kErrEmptyWait);
+      const uint32_t row_bytes = U.ncols * 4, meta_bytes = U.ncols * 2;
+      if (lane == 0) mbar_arrive_expect_tx(&S.full[st], U.nrows * row_bytes + 2 * U.ng * meta_bytes);
+      __syncwarp();
+      const uint32_t* src = I.wq + static_cast<size_t>(U.wr0) * J.N + U.n0;
+      for (int r = lane; r < U.nrows; r += 32)
+        bulk_g2s(B.words + r * kRowPitch, src + static_cast<size_t>(r) * J.N, row_bytes, &S.full[st]);
+      for (int gi = lane; gi < 2 * U.ng; gi += 32) {
+        const int gq = gi >> 1;
+        const __half* msrc = ((gi & 1) ? I.zeros : I.scales) + static_cast<size_t>(U.g0 + gq) * J.N + U.n0;
+        bulk_g2s((gi & 1) ? B.zeros[gq] : B.scales[gq], msrc, meta_bytes, &S.full[st]);
+      }
+    }
+  }
+}
+
+// ---- activation tables ----------------------------------------------------------------
+// c = 14 - floor(log2(max|x|)) of a group: the largest value lands in [2^14, 2^15).
+__device__ __forceinline__ int scale_exponent(float mx) {
+  int c = 14 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
+  return c < -15 ? -15 : (c > 40 ? 40 : c);
+}
+
+// 1/2/4-bit: lane handles word rows `lane` and `lane + 32`.  A group is 4*B consecutive rows,
+// so its maximum and sum are reductions over 4*B neighbouring lanes.
+template <int B, bool XF32>
+__device__ __forceinline__ void build_table_pow2(StageBuf& T, const void* x, const Unit& U) {
+  constexpr int EPS = 32 / B, PAIRS = EPS / 2, NPOS = 10 / B, LPG = 4 * B;
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int row = lane + 32 * rr;
+    const bool on = row < U.nrows;
+    float xv[EPS];
+    if (on) {
+      const size_t k = static_cast<size_t>(U.g0) * kGroup + static_cast<size_t>(row) * EPS;
+      if (XF32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + k);
+#pragma unroll
+        for (int i = 0; i < EPS / 4; ++i) {
+          const float4 t = p[i];
+          xv[4 * i] = t.x; xv[4 * i + 1] = t.y; xv[4 * i + 2] = t.z; xv[4 * i + 3] = t.w;
+        }
+      } else {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(x) + k);
+#pragma unroll
+        for (int i = 0; i < EPS / 8; ++i) {
+          const uint4 t = p[i];
+          const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __half22float2(h[q]);
+            xv[8 * i + 2 * q] = f.x; xv[8 * i + 2 * q + 1] = f.y;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPS; ++i) xv[i] = 0.f;
+    }
+    float mx = 0.f, sm = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPS; ++i) { mx = fmaxf(mx, fabsf(xv[i])); sm += xv[i]; }
+#pragma unroll
+    for (int o = 1; o < LPG; o <<= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      sm += __shfl_xor_sync(0xffffffffu, sm, o);
+    }
+    const int c = scale_exponent(mx);
+    if (on && (lane % LPG) == 0) {
+      T.xsum[row / LPG] = sm;
+      T.fin[row / LPG] = pow2i(24 - c);
+    }
+    if (on) {
+      uint32_t outw[PAIRS];
+#pragma unroll
+      for (int q = 0; q < PAIRS; ++q) {
+        const float f = pow2i(c - B * (q % NPOS));
+        const __half2 h = __floats2half2_rn(xv[q] * f, xv[q + PAIRS] * f);
+        outw[q] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(T.tab + row * PAIRS);
+#pragma unroll
+      for (int i = 0; i < PAIRS / 4; ++i) dst[i] = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+    }
+  }
+}
+
+// 3-bit: element-wise, one group (128 elements, 4 per lane) at a time.
+template <bool XF32>
+__device__ __forceinline__ void build_table_b3(StageBuf& T, const void* x, const Unit& U) {
+  const int lane = threadIdx.x & 31;
+  uint4* z4 = reinterpret_cast<uint4*>(T.tab);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) z4[lane + 32 * i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncwarp();
+  __half* tab = reinterpret_cast<__half*>(T.tab);
+  for (int gq = 0; gq < U.ng; ++gq) {
+    float xv[4];
+    float mx = 0.f, sm = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const size_t k = static_cast<size_t>(U.g0 + gq) * kGroup + i * 32 + lane;
+      xv[i] = XF32 ? static_cast<const float*>(x)[k] : __half2float(static_cast<const __half*>(x)[k]);
+      mx = fmaxf(mx, fabsf(xv[i]));
+      sm += xv[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      sm += __shfl_xor_sync(0xffffffffu, sm, o);
+    }
+    const int c = scale_exponent(mx);
+    if (lane == 0) {
+      T.xsum[gq] = sm;
+      T.fin[gq] = pow2i(24 - c);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = gq * kGroup + i * 32 + lane;
+      const int row = e / 10, j = e - row * 10;
+      const int hi = j >= 5 ? 1 : 0, q = j - 5 * hi;
+      const int variant = (gq != ((row * 10) >> 7)) ? 1 : 0;
+      const int pos = 3 * (q < 3 ? q : q - 3);
+      tab[variant * 1024 + row * 16 + 2 * q + hi] = __float2half_rn(xv[i] * pow2i(c - pos));
+    }
+  }
+}
+
+template <bool XF32>
+__device__ void table_role(StreamSmem& S, const GemvParams& P, int* err) {
+  const int lane = threadIdx.x & 31;
+  PartWalk W;
+  W.begin(S);
+  Part Pt;
+  int it = 0;
+  while (W.next(S, Pt)) {
+    const GemvJob& J = P.jobs[Pt.job];
+    const JobInfo& I = S.info[Pt.job];
+    for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
+      Unit U;
+      make_unit(J, I, Pt.job, sl, Pt.chunk, U);
+      const int st = it % kSStages;
+      mbar_wait(&S.empty[st], ((it / kSStages) & 1) ^ 1, err, kErrEmptyWait);
+      StageBuf& T = S.stage[st];
+      if (U.bits == 1) build_table_pow2<1, XF32>(T, J.xa, U);
+      else if (U.bits == 2) build_table_pow2<2, XF32>(T, J.xa, U);
+      else if (U.bits == 3) build_table_b3<XF32>(T, J.xa, U);
+      else build_table_pow2<4, XF32>(T, J.xa, U);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.full[st]);
+    }
+  }
+}
+
+// ---- consumers --------------------------------------------------------------------------
+template <int B>
+struct SFmt {
+  static constexpr int kEps = 32 / B;
+  static constexpr int kPairs = kEps / 2;
+  static constexpr int kPos = 10 / B;
+  static constexpr int kMma = kEps / 4;
+  static constexpr uint32_t kMask = ((1u << B) - 1u) * 0x00010001u;
+  // fp16x2 operand number q of a word: codes q (low half) and q + eps/2 (high half), in place
+  __device__ static __forceinline__ uint32_t operand(uint32_t w, int q) {
+    const int stage = q / kPos, jj = q % kPos;
+    return (w >> (stage * kPos * B)) & (kMask << (B * jj));
+  }
+};
+
+__device__ __forceinline__ void apply_group(const StageBuf& Sg, int gu, int col, float xs, const float (&acc)[2][4],
+                                            int p, float (&vs)[2][4]) {
+  const uint2 sr = *reinterpret_cast<const uint2*>(&Sg.scales[gu][col]);
+  const uint2 zr = *reinterpret_cast<const uint2*>(&Sg.zeros[gu][col]);
+  const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sr.x));
+  const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sr.y));
+  const float2 z01 = __half22float2(*reinterpret_cast<const __half2*>(&zr.x));
+  const float2 z23 = __half22float2(*reinterpret_cast<const __half2*>(&zr.y));
+  const float fin = Sg.fin[gu];
+  vs[0][p] += fmaf(s01.x * fin, acc[0][p], z01.x * xs);
+  vs[0][2 + p] += fmaf(s01.y * fin, acc[0][2 + p], z01.y * xs);
+  vs[1][p] += fmaf(s23.x * fin, acc[1][p], z23.x * xs);
+  vs[1][2 + p] += fmaf(s23.y * fin, acc[1][2 + p], z23.y * xs);
+}
+
+// Rows [16*kp, 16*kp+16) of the unit, columns 32*cw + 4*g .. +3; adds into vs.
+template <int B>
+__device__ __forceinline__ void consume_pow2(const StageBuf& Sg, const uint32_t* zero_row, const Unit& U, int cw,
+                                             int kp, float (&vs)[2][4]) {
+  using F = SFmt<B>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  float acc[2][4];
+#pragma unroll
+  for (int s = 0; s < 2; ++s)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[s][e] = 0.f;
+  const unsigned char* wbase = Sg.words + (16 * kp + c) * kRowPitch + (32 * cw + 4 * g) * 4;
+  uint4 w4[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (16 * kp + 4 * i < U.nrows) w4[i] = *reinterpret_cast<const uint4*>(wbase + i * 4 * kRowPitch);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (16 * kp + 4 * i < U.nrows) {
+      const int row = 16 * kp + 4 * i + c;
+      const uint32_t* bp = (g == i / B) ? Sg.tab + row * F::kPairs : zero_row;
+      uint32_t bf[F::kPairs];
+#pragma unroll
+      for (int q4 = 0; q4 < F::kPairs / 4; ++q4) {
+        const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
+        bf[4 * q4 + 0] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
+      }
+      const uint32_t wv[4] = {w4[i].x, w4[i].y, w4[i].z, w4[i].w};
+#pragma unroll
+      for (int m = 0; m < F::kMma; ++m)
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+          mma16816s(acc[s], F::operand(wv[2 * s], 2 * m), F::operand(wv[2 * s + 1], 2 * m),
+                    F::operand(wv[2 * s], 2 * m + 1), F::operand(wv[2 * s + 1], 2 * m + 1), bf[2 * m], bf[2 * m + 1]);
+    }
+  }
+  // C column 2c+p carries group 2c+p of this row quarter (4/B groups per quarter)
+  constexpr int GPQ = 4 / B;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int d = 2 * c + p;
+    const int gu = kp * GPQ + d;
+    if (d < GPQ && gu < U.ng) apply_group(Sg, gu, 32 * cw + 4 * g, Sg.xsum[gu], acc, p, vs);
+  }
+}
+
+// 3-bit: 10 codes per word; a 640-wide unit is word aligned, its five groups ride in MMA
+// columns 0..4.  A word that straddles two groups appears in two table variants.
+struct S3Fmt {
+  __device__ static __forceinline__ uint32_t merge(uint32_t w) { return (w & 0x00007fffu) | ((w << 1) & 0x7fff0000u); }
+  __device__ static __forceinline__ uint32_t operand(uint32_t t, int q) {
+    return q < 3 ? (t & (0x00070007u << (3 * q))) : ((t >> 9) & (0x00070007u << (3 * (q - 3))));
+  }
+};
+
+__device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* zero_row, const Unit& U, int cw,
+                                           int kp, float (&vs)[2][4]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  float acc[2][4];
+#pragma unroll
+  for (int s = 0; s < 2; ++s)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[s][e] = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (16 * kp + 8 * i < U.nrows) {
+      uint32_t mw[2][4];
+      uint32_t bf[10];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = 16 * kp + 8 * i + 2 * c + r;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (row < U.nrows) w = *reinterpret_cast<const uint4*>(Sg.words + row * kRowPitch + (32 * cw + 4 * g) * 4);
+        mw[r][0] = S3Fmt::merge(w.x); mw[r][1] = S3Fmt::merge(w.y);
+        mw[r][2] = S3Fmt::merge(w.z); mw[r][3] = S3Fmt::merge(w.w);
+        const int d0 = (row * 10) >> 7;
+        const uint32_t* bp = zero_row;
+        if (g == d0) bp = Sg.tab + row * 8;
+        else if (g == d0 + 1) bp = Sg.tab + 512 + row * 8;
+        const uint4 t4 = *reinterpret_cast<const uint4*>(bp);
+        bf[5 * r + 0] = t4.x; bf[5 * r + 1] = t4.y; bf[5 * r + 2] = t4.z; bf[5 * r + 3] = t4.w;
+        bf[5 * r + 4] = bp[4];
+      }
+#pragma unroll
+      for (int m = 0; m < 5; ++m)
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          const int s0 = 2 * m, s1 = 2 * m + 1;
+          const uint32_t a0 = s0 < 5 ? S3Fmt::operand(mw[0][2 * s], s0) : S3Fmt::operand(mw[1][2 * s], s0 - 5);
+          const uint32_t a1 = s0 < 5 ? S3Fmt::operand(mw[0][2 * s + 1], s0) : S3Fmt::operand(mw[1][2 * s + 1], s0 - 5);
+          const uint32_t a2 = s1 < 5 ? S3Fmt::operand(mw[0][2 * s], s1) : S3Fmt::operand(mw[1][2 * s], s1 - 5);
+          const uint32_t a3 = s1 < 5 ? S3Fmt::operand(mw[0][2 * s + 1], s1) : S3Fmt::operand(mw[1][2 * s + 1], s1 - 5);
+          mma16816s(acc[s], a0, a1, a2, a3, bf[s0], bf[s1]);
+        }
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int d = 2 * c + p;  // unit-local group carried by C column d
+    // groups are not aligned to the row quarters: the offset term is added once, by quarter 0
+    if (d < 5 && d < U.ng) apply_group(Sg, d, 32 * cw + 4 * g, kp == 0 ? Sg.xsum[d] : 0.f, acc, p, vs);
+  }
+}
+
+__device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cw = warp & 3, kp = warp >> 2;
+  const int g = lane >> 2, c = lane & 3;
+  PartWalk W;
+  W.begin(S);
+  Part Pt;
+  int it = 0, pc = 0;
+  while (W.next(S, Pt)) {
+    const GemvJob& J = P.jobs[Pt.job];
+    const JobInfo& I = S.info[Pt.job];
+    float vs[2][4];
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) vs[s][e] = 0.f;
+    for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
+      Unit U;
+      make_unit(J, I, Pt.job, sl, Pt.chunk, U);
+      const int st = it % kSStages;
+      const StageBuf& B = S.stage[st];
+      mbar_wait(&S.full[st], (it / kSStages) & 1, err, kErrFullWait);
+      if (32 * cw < U.ncols && 16 * kp < U.nrows) {
+        if (U.bits == 1) consume_pow2<1>(B, S.zero_row, U, cw, kp, vs);
+        else if (U.bits == 2) consume_pow2<2>(B, S.zero_row, U, cw, kp, vs);
+        else if (U.bits == 3) consume_b3(B, S.zero_row, U, cw, kp, vs);
+        else consume_pow2<4>(B, S.zero_row, U, cw, kp, vs);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.empty[st]);
+    }
+    // end of the part: sum the 8 MMA columns (= groups) and hand the strip to the finisher
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      vs[s][0] += vs[s][1];
+      vs[s][2] += vs[s][3];
+#pragma unroll
+      for (int o = 1; o <= 2; o <<= 1) {
+        vs[s][0] += __shfl_xor_sync(0xffffffffu, vs[s][0], o);
+        vs[s][2] += __shfl_xor_sync(0xffffffffu, vs[s][2], o);
+      }
+    }
+    const int slot = pc % kRedSlots;
+    mbar_wait(&S.redempty[slot], ((pc / kRedSlots) & 1) ^ 1, err, kErrRedEmptyWait);
+    if (c == 0)
+      *reinterpret_cast<float4*>(&S.red[slot][kp][32 * cw + 4 * g]) = make_float4(vs[0][0], vs[0][2], vs[1][0], vs[1][2]);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&S.redfull[slot]);
+    ++pc;
+  }
+}
+
+// ---- finisher -----------------------------------------------------------------------------
+// Sum the partial slots of one job's chunk columns n..n+3 in slice order and restore them to zero.
+__device__ __forceinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J, int slices, int n) {
+  float* src = P.partial + J.col_base + n;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < slices; ++s) {
+    float4* q = reinterpret_cast<float4*>(src + static_cast<size_t>(s) * P.c_total);
+    const float4 t = __ldcg(q);
+    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+    __stcg(q, make_float4(0.f, 0.f, 0.f, 0.f));
+  }
+  return sum;
+}
+
+__device__ __forceinline__ void store_half4(__half* dst, const float4& v) {
+  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&lo);
+  o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = o;
+}
+
+__device__ __forceinline__ float4 round_half4(const float4& v) {
+  return make_float4(__half2float(__float2half_rn(v.x)), __half2float(__float2half_rn(v.y)),
+                     __half2float(__float2half_rn(v.z)), __half2float(__float2half_rn(v.w)));
+}
+
+__device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Part& Pt, int n) {
+  if (P.epi == kEpiStore) {
+    const GemvJob& J = P.jobs[Pt.job];
+    store_half4(J.y + n, drain_slots(P, J, S.info[Pt.job].slices, n));
+  } else if (P.epi == kEpiUpPair) {
+    const int j1 = Pt.job & ~1, j3 = j1 + 1;
+    const GemvJob& J1 = P.jobs[j1];
+    const GemvJob& J3 = P.jobs[j3];
+    const float4 a = round_half4(drain_slots(P, J1, S.info[j1].slices, n));
+    const float4 b = round_half4(drain_slots(P, J3, S.info[j3].slices, n));
+    if (J1.y) store_half4(J1.y + n, a);
+    if (J3.y) store_half4(J3.y + n, b);
+    if (J1.h)
+      *reinterpret_cast<float4*>(J1.h + n) =
+          make_float4(silu_f32(a.x) * b.x, silu_f32(a.y) * b.y, silu_f32(a.z) * b.z, silu_f32(a.w) * b.w);
+  } else {
+    float4 accw = make_float4(0.f, 0.f, 0.f, 0.f), res = accw;
+    for (int i = 0; i < P.n_jobs; ++i) {
+      const GemvJob& Ji = P.jobs[i];
+      const float4 x2 = round_half4(drain_slots(P, Ji, S.info[i].slices, n));
+      if (Ji.y) store_half4(Ji.y + n, x2);
+      if (i < P.comb_weighted) {
+        const float wgt = __half2float(P.comb_w[i]);
+        accw.x = fmaf(wgt, x2.x, accw.x); accw.y = fmaf(wgt, x2.y, accw.y);
+        accw.z = fmaf(wgt, x2.z, accw.z); accw.w = fmaf(wgt, x2.w, accw.w);
+        if (i == P.comb_weighted - 1) res = round_half4(accw);
+      } else {
+        res = round_half4(make_float4(res.x + x2.x, res.y + x2.y, res.z + x2.z, res.w + x2.w));
+      }
+    }
+    store_half4(P.comb_out + n, res);
+  }
+}
+
+__device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
+  const int lane = threadIdx.x & 31;
+  PartWalk W;
+  W.begin(S);
+  Part Pt;
+  for (int pc = 0; W.next(S, Pt); ++pc) {
+    const GemvJob& J = P.jobs[Pt.job];
+    const JobInfo& I = S.info[Pt.job];
+    const int slot = pc % kRedSlots;
+    mbar_wait(&S.redfull[slot], (pc / kRedSlots) & 1, err, kErrRedFullWait);
+    float4 r = *reinterpret_cast<const float4*>(&S.red[slot][0][4 * lane]);
+#pragma unroll
+    for (int q = 1; q < 4; ++q) {
+      const float4 t = *reinterpret_cast<const float4*>(&S.red[slot][q][4 * lane]);
+      r.x += t.x; r.y += t.y; r.z += t.z; r.w += t.w;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&S.redempty[slot]);
+
+    const int n0 = Pt.chunk * 128;
+    const int ncols = min(128, J.N - n0);
+    const bool col_on = 4 * lane < ncols;
+    const int n = n0 + 4 * lane;
+    const bool whole = Pt.sa == 0 && Pt.sb == I.slices;
+    if (whole && P.epi == kEpiStore) {
+      if (col_on) store_half4(J.y + n, r);
+      continue;
+    }
+    if (col_on) {
+      __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(Pt.sa) * P.c_total + J.col_base + n), r);
+      __threadfence();
+    }
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      int expected = I.slices;
+      int* ctr = P.counters + J.chunk_base + Pt.chunk;
+      if (P.epi == kEpiUpPair) expected = S.info[Pt.job & ~1].slices + S.info[(Pt.job & ~1) + 1].slices;
+      if (P.epi == kEpiCombine) {
+        expected = 0;
+        for (int i = 0; i < P.n_jobs; ++i) expected += S.info[i].slices;
+      }
+      const int add = Pt.sb - Pt.sa;
+      const int old = atomicAdd(ctr, add);
+      last = (old + add == expected);
+      if (last) *ctr = 0;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence();
+      if (col_on) finish_group(S, P, Pt, n);
+    }
+  }
+}
+
+template <bool XF32>
+__global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_constant__ GemvParams P) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  StreamSmem& S = *reinterpret_cast<StreamSmem*>(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  int* err = P.counters + kErrSlot;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSStages; ++s) {
+      mbar_init(&S.full[s], 2);  // producer (with the byte count) + table warp
+      mbar_init(&S.empty[s], kSConsumers);
+    }
+    for (int s = 0; s < kRedSlots; ++s) {
+      mbar_init(&S.redfull[s], kSConsumers);
+      mbar_init(&S.redempty[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 16) S.zero_row[threadIdx.x] = 0u;
+  if (warp == 0) make_plan(S, P);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  if (warp < kSConsumers) consumer_role(S, P, err);
+  else if (warp == kWarpProducer) producer_role(S, P, err);
+  else if (warp == kWarpTable) table_role<XF32>(S, P, err);
+  else finisher_role(S, P, err);
+  __syncthreads();
+}
+
+// h[i] = silu(x1[i]) * x3[i] in fp32 (gemq/triton_kernels/fused_dequant_bmm.py:237-239)
+__global__ void silu_mul_kernel(const __half* __restrict__ x1, const __half* __restrict__ x3, float* __restrict__ h, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) h[i] = silu_f32(__half2float(x1[i])) * __half2float(x3[i]);
+}
+
+// ---- host ---------------------------------------------------------------------------------
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <bool XF32>
+static int launch_stream_t(GemvParams& P, cudaStream_t stream, int units_bound) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const size_t smem = sizeof(StreamSmem);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemv_stream_kernel<XF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return GEMQ_ERR_LAUNCH;
+    attr_set[dev] = true;
+  }
+  const int sms = sm_count();
+  if (sms <= 0) return GEMQ_ERR_LAUNCH;
+  const int grid = units_bound < sms ? units_bound : sms;
+  gemv_stream_kernel<XF32><<<grid, kSThreads, smem, stream>>>(P);
+  return launch_status();
+}
+
+int silu_mul_f32(const __half* x1, const __half* x3, float* h, int n, cudaStream_t stream) {
+  silu_mul_kernel<<<cdiv(n, 256), 256, 0, stream>>>(x1, x3, h, n);
+  return launch_status();
+}
+
+// One activation row; every job N % 32 == 0, K % 128 == 0, group 128, activations 16-byte
+// aligned.  P.epi / P.x_f32 select epilogue and activation type; kEpiUpPair expects the
+// jobs in (gate, up) pairs.
+int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* counters, cudaStream_t stream) {
+  int cols = 0, chunks = 0, max_slices = 0, units = 0;
+  for (int i = 0; i < P.n_jobs; ++i) {
+    GemvJob& J = P.jobs[i];
+    const int nch = cdiv(J.N, 128);
+    J.col_base = cols;
+    J.tile_base = 0;
+    cols += J.N;
+    if (P.epi == kEpiStore) {
+      J.chunk_base = chunks;
+      chunks += nch;
+    } else if (P.epi == kEpiUpPair) {
+      J.chunk_base = chunks;
+      if (i & 1) chunks += nch;
+    } else {
+      J.chunk_base = 0;
+      chunks = nch;
+    }
+    const int slices = cdiv(J.K / kGroup, 4);  // 4-bit units are the shortest: 4 groups
+    max_slices = slices > max_slices ? slices : max_slices;
+    units += nch * cdiv(J.K / kGroup, 16);     // at least this many (1-bit units: 16 groups)
+  }
+  if (P.epi == kEpiUpPair && (P.n_jobs & 1)) return GEMQ_ERR_BAD_ARG;
+  if (chunks >= kErrSlot) return GEMQ_ERR_WORKSPACE;
+  if (static_cast<size_t>(max_slices) * cols > partial_floats) return GEMQ_ERR_WORKSPACE;
+  P.c_total = cols;
+  P.n_chunks = chunks;
+  P.s_max = max_slices;
+  P.G = kGroup;
+  P.partial = partial;
+  P.counters = counters;
+  return P.x_f32 ? launch_stream_t<true>(P, stream, units) : launch_stream_t<false>(P, stream, units);
+}
+
+}  // namespace gemq

@@ -8,8 +8,7 @@ namespace gemq {
 struct DecodeScratch {
   void* gemv_ws;
   size_t gemv_ws_bytes;
-  __half* x1;  // [A*F + shared_ffn]
-  __half* x3;
+  float* h;  // [A*F + shared_ffn] fp32 silu(x1) * x3, written by the gate/up epilogue
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -24,13 +23,12 @@ static size_t decode_ws_bytes(const gemq_moe_layer_t* L) {
 
 static bool carve(const gemq_moe_layer_t* L, void* scratch, size_t bytes, DecodeScratch* S) {
   const size_t ws = decode_ws_bytes(L);
-  const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(__half), 256);
-  if (!scratch || bytes < ws + 2 * act || !aligned16(scratch)) return false;
+  const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(float), 256);
+  if (!scratch || bytes < ws + act || !aligned16(scratch)) return false;
   char* p = static_cast<char*>(scratch);
   S->gemv_ws = p;
   S->gemv_ws_bytes = ws;
-  S->x1 = reinterpret_cast<__half*>(p + ws);
-  S->x3 = reinterpret_cast<__half*>(p + ws + act);
+  S->h = reinterpret_cast<float*>(p + ws);
   return true;
 }
 
@@ -61,8 +59,8 @@ using namespace gemq;
 
 extern "C" size_t gemq_moe_decode_scratch_bytes(const gemq_moe_layer_t* L) {
   if (!L || L->hidden <= 0 || L->ffn <= 0 || L->top_k <= 0) return 0;
-  const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(__half), 256);
-  return decode_ws_bytes(L) + 2 * act;
+  const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(float), 256);
+  return decode_ws_bytes(L) + act;
 }
 
 extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* out,
@@ -101,7 +99,7 @@ extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* o
         }
         J.xa = xt;
         J.ldx = D;
-        J.y = (m ? S.x3 : S.x1) + static_cast<size_t>(a) * F;
+        if (!m) J.h = S.h + static_cast<size_t>(a) * F;
       }
     }
     if (SF > 0) {
@@ -110,10 +108,11 @@ extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* o
         single_job(J, m ? L->s3 : L->s1, SF, D);
         J.xa = xt;
         J.ldx = D;
-        J.y = (m ? S.x3 : S.x1) + static_cast<size_t>(A) * F;
+        if (!m) J.h = S.h + static_cast<size_t>(A) * F;
       }
     }
     P.n_jobs = nj;
+    P.epi = kEpiUpPair;
     int rc = run_gemv_jobs(P, false, kGroup, S.gemv_ws, S.gemv_ws_bytes, st);
     if (rc) return rc;
 
@@ -124,20 +123,20 @@ extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* o
     for (int a = 0; a < A; ++a) {
       GemvJob& J = Q.jobs[nj++];
       stacked_job(J, L->w2, idx_t + a, D, F);
-      J.xa = S.x1 + static_cast<size_t>(a) * F;
-      J.xb = S.x3 + static_cast<size_t>(a) * F;
+      J.xa = reinterpret_cast<const __half*>(S.h + static_cast<size_t>(a) * F);
     }
     if (SF > 0) {
       GemvJob& J = Q.jobs[nj++];
       single_job(J, L->s2, D, SF);
-      J.xa = S.x1 + static_cast<size_t>(A) * F;
-      J.xb = S.x3 + static_cast<size_t>(A) * F;
+      J.xa = reinterpret_cast<const __half*>(S.h + static_cast<size_t>(A) * F);
     }
     Q.n_jobs = nj;
+    Q.epi = kEpiCombine;
+    Q.x_f32 = 1;
     Q.comb_out = static_cast<__half*>(out) + static_cast<size_t>(t) * D;
     Q.comb_w = static_cast<const __half*>(w) + static_cast<size_t>(t) * A;
     Q.comb_weighted = A;
-    rc = run_gemv_jobs(Q, true, kGroup, S.gemv_ws, S.gemv_ws_bytes, st);
+    rc = run_gemv_jobs(Q, false, kGroup, S.gemv_ws, S.gemv_ws_bytes, st);
     if (rc) return rc;
   }
   return GEMQ_OK;
