@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libgemq_b200.so")
+LIB_PATH = os.environ.get("GEMQ_B200_LIB") or os.path.join(_HERE, "libgemq_b200.so")
 
 ERRORS = {
     -1: "bad argument (null pointer, non-positive extent or unsupported bit-width)",
@@ -28,7 +28,8 @@ class GemqError(RuntimeError):
 
 class Stacked(C.Structure):
     _fields_ = [("wq", C.c_void_p), ("scales", C.c_void_p), ("zeros", C.c_void_p),
-                ("nbits", C.c_void_p), ("wq_strides", C.c_void_p), ("zs_strides", C.c_void_p)]
+                ("nbits", C.c_void_p), ("wq_strides", C.c_void_p), ("zs_strides", C.c_void_p),
+                ("wq_rows", C.c_int64), ("zs_rows", C.c_int64)]
 
 
 class Single(C.Structure):
@@ -53,10 +54,10 @@ _SIGNATURES = {
     "gemq_unpack_over_cols": (_I, [_P, _P, _I, _I, _I, _I, _P]),
     "gemq_dequantize": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "gemq_dequant_gemv": (_I, [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _Z, _P]),
-    "gemq_dequant_sel_gemv": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
-    "gemq_fused_up_proj": (_I, [_P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
-    "gemq_fused_down_proj": (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
-    "gemq_dequant_group_gemv": (_I, [_P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
+    "gemq_dequant_sel_gemv": (_I, [_P, _P, C.POINTER(Stacked), _P, _I, _I, _I, _P, _Z, _P]),
+    "gemq_fused_up_proj": (_I, [_P, _P, _I, C.POINTER(Stacked), C.POINTER(Stacked), _P, _P, _I, _I, _I, _P, _Z, _P]),
+    "gemq_fused_down_proj": (_I, [_P, _P, _P, _I, C.POINTER(Stacked), _P, _I, _I, _I, _P, _Z, _P]),
+    "gemq_dequant_group_gemv": (_I, [_P, _I, _P, _I, C.POINTER(Stacked), _P, _I, _I, _I, _I, _P, _Z, _P]),
     "gemq_moe_route": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
     "gemq_moe_decode_scratch_bytes": (_Z, [C.POINTER(MoeLayer)]),
     "gemq_moe_decode": (_I, [C.POINTER(MoeLayer), _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
@@ -79,6 +80,12 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
+
+
+def stacked(wq, scales, zeros, nbits, wq_strides, zs_strides=None) -> Stacked:
+    """Describe stacked-expert torch tensors for the library (borrowed pointers)."""
+    return Stacked(wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(), nbits.data_ptr(), wq_strides.data_ptr(),
+                   zs_strides.data_ptr() if zs_strides is not None else None, wq.shape[0], scales.shape[0])
 
 
 def check(fn: str, code: int) -> None:

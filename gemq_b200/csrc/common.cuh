@@ -1,6 +1,7 @@
 // Shared helpers of the gemq_b200 kernels (sm_100a).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>

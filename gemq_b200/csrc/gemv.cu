@@ -719,6 +719,24 @@ extern "C" size_t gemq_gemv_workspace_bytes(int total_cols, int max_k, int token
 
 static bool bits_ok(int b) { return b >= 1 && b <= 4; }
 
+static void job_from_stacked(GemvJob& J, const gemq_stacked_t* W, const int64_t* idx_slot, int N, int K) {
+  J.wq = reinterpret_cast<const uint32_t*>(W->wq);
+  J.scales = static_cast<const __half*>(W->scales);
+  J.zeros = static_cast<const __half*>(W->zeros);
+  J.nbits = W->nbits;
+  J.wq_strides = W->wq_strides;
+  J.zs_strides = W->zs_strides;
+  J.idx = reinterpret_cast<const long long*>(idx_slot);
+  J.wq_rows = W->wq_rows;
+  J.zs_rows = W->zs_rows;
+  J.N = N;
+  J.K = K;
+}
+
+static bool stacked_ok(const gemq_stacked_t* W) {
+  return W && W->wq && W->scales && W->zeros && W->nbits && W->wq_strides && W->wq_rows > 0 && W->zs_rows > 0;
+}
+
 extern "C" int gemq_dequant_gemv(const void* x, int ldx, const int32_t* wq, const void* scales, const void* zeros,
                                  void* y, int ldy, int tokens, int N, int K, int nbits, int group_size,
                                  void* workspace, size_t workspace_bytes, gemq_stream_t stream) {
@@ -735,40 +753,32 @@ extern "C" int gemq_dequant_gemv(const void* x, int ldx, const int32_t* wq, cons
   J.xa = static_cast<const __half*>(x);
   J.y = static_cast<__half*>(y);
   J.N = N; J.K = K; J.ldx = ldx; J.ldy = ldy;
+  J.wq_rows = cdiv(K, 32 / nbits);
+  J.zs_rows = K / group_size;
   return run_gemv_jobs(P, false, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int gemq_dequant_sel_gemv(const void* x, const int64_t* idx, const int32_t* wq, const void* scales,
-                                     const void* zeros, const int32_t* nbits, const int32_t* wq_strides,
+extern "C" int gemq_dequant_sel_gemv(const void* x, const int64_t* idx, const gemq_stacked_t* w,
                                      void* y, int N, int K, int group_size,
                                      void* workspace, size_t workspace_bytes, gemq_stream_t stream) {
-  if (!x || !idx || !wq || !scales || !zeros || !nbits || !wq_strides || !y || N <= 0 || K <= 0 || group_size <= 0)
-    return GEMQ_ERR_BAD_ARG;
+  if (!x || !idx || !stacked_ok(w) || !y || N <= 0 || K <= 0 || group_size <= 0) return GEMQ_ERR_BAD_ARG;
   GemvParams P = {};
   P.n_jobs = 1;
   P.T = 1;
   GemvJob& J = P.jobs[0];
-  J.wq = reinterpret_cast<const uint32_t*>(wq);
-  J.scales = static_cast<const __half*>(scales);
-  J.zeros = static_cast<const __half*>(zeros);
-  J.nbits = nbits;
-  J.wq_strides = wq_strides;
-  J.idx = reinterpret_cast<const long long*>(idx);
+  job_from_stacked(J, w, idx, N, K);
+  J.zs_strides = nullptr;
   J.xa = static_cast<const __half*>(x);
   J.y = static_cast<__half*>(y);
-  J.N = N; J.K = K; J.ldx = K; J.ldy = N;
+  J.ldx = K; J.ldy = N;
   return run_gemv_jobs(P, false, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int gemq_fused_up_proj(const void* x, const int64_t* idx, int A,
-                                  const int32_t* w1, const int32_t* w3,
-                                  const void* w1_scales, const void* w1_zeros,
-                                  const void* w3_scales, const void* w3_zeros,
-                                  const int32_t* nbits, const int32_t* w_strides,
+                                  const gemq_stacked_t* w1, const gemq_stacked_t* w3,
                                   void* x1, void* x3, int N, int K, int group_size,
                                   void* workspace, size_t workspace_bytes, gemq_stream_t stream) {
-  if (!x || !idx || !w1 || !w3 || !w1_scales || !w1_zeros || !w3_scales || !w3_zeros || !nbits || !w_strides ||
-      !x1 || !x3 || A <= 0 || N <= 0 || K <= 0 || group_size <= 0)
+  if (!x || !idx || !stacked_ok(w1) || !stacked_ok(w3) || !x1 || !x3 || A <= 0 || N <= 0 || K <= 0 || group_size <= 0)
     return GEMQ_ERR_BAD_ARG;
   if (A > kMaxSlots) return GEMQ_ERR_BAD_SHAPE;
   GemvParams P = {};
@@ -777,15 +787,13 @@ extern "C" int gemq_fused_up_proj(const void* x, const int64_t* idx, int A,
   for (int a = 0; a < A; ++a) {
     for (int m = 0; m < 2; ++m) {
       GemvJob& J = P.jobs[2 * a + m];
-      J.wq = reinterpret_cast<const uint32_t*>(m ? w3 : w1);
-      J.scales = static_cast<const __half*>(m ? w3_scales : w1_scales);
-      J.zeros = static_cast<const __half*>(m ? w3_zeros : w1_zeros);
-      J.nbits = nbits;
-      J.wq_strides = w_strides;
-      J.idx = reinterpret_cast<const long long*>(idx) + a;
+      job_from_stacked(J, m ? w3 : w1, idx + a, N, K);
+      J.nbits = w1->nbits;
+      J.wq_strides = w1->wq_strides;
+      J.zs_strides = nullptr;
       J.xa = static_cast<const __half*>(x);
       J.y = static_cast<__half*>(m ? x3 : x1) + static_cast<size_t>(a) * N;
-      J.N = N; J.K = K; J.ldx = K; J.ldy = A * N;
+      J.ldx = K; J.ldy = A * N;
     }
   }
   P.epi = kEpiUpPair;
@@ -793,12 +801,10 @@ extern "C" int gemq_fused_up_proj(const void* x, const int64_t* idx, int A,
 }
 
 extern "C" int gemq_fused_down_proj(const void* x1, const void* x3, const int64_t* idx, int A,
-                                    const int32_t* w2, const void* w2_scales, const void* w2_zeros,
-                                    const int32_t* nbits, const int32_t* w_strides,
+                                    const gemq_stacked_t* w2,
                                     void* x2, int N, int K, int group_size,
                                     void* workspace, size_t workspace_bytes, gemq_stream_t stream) {
-  if (!x1 || !x3 || !idx || !w2 || !w2_scales || !w2_zeros || !nbits || !w_strides || !x2 || A <= 0 || N <= 0 ||
-      K <= 0 || group_size <= 0)
+  if (!x1 || !x3 || !idx || !stacked_ok(w2) || !x2 || A <= 0 || N <= 0 || K <= 0 || group_size <= 0)
     return GEMQ_ERR_BAD_ARG;
   if (A > kMaxSlots) return GEMQ_ERR_BAD_SHAPE;
   GemvParams P = {};
@@ -806,27 +812,22 @@ extern "C" int gemq_fused_down_proj(const void* x1, const void* x3, const int64_
   P.T = 1;
   for (int a = 0; a < A; ++a) {
     GemvJob& J = P.jobs[a];
-    J.wq = reinterpret_cast<const uint32_t*>(w2);
-    J.scales = static_cast<const __half*>(w2_scales);
-    J.zeros = static_cast<const __half*>(w2_zeros);
-    J.nbits = nbits;
-    J.wq_strides = w_strides;
-    J.idx = reinterpret_cast<const long long*>(idx) + a;
+    job_from_stacked(J, w2, idx + a, N, K);
+    J.zs_strides = nullptr;
     J.xa = static_cast<const __half*>(x1) + static_cast<size_t>(a) * K;
     J.xb = static_cast<const __half*>(x3) + static_cast<size_t>(a) * K;
     J.y = static_cast<__half*>(x2) + static_cast<size_t>(a) * N;
-    J.N = N; J.K = K; J.ldx = A * K; J.ldy = A * N;
+    J.ldx = A * K; J.ldy = A * N;
   }
   return run_gemv_jobs(P, true, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int gemq_dequant_group_gemv(const void* x, int ldx, const int64_t* indices, int A,
-                                       const int32_t* wq, const void* scales, const void* zeros,
-                                       const int32_t* nbits, const int32_t* wq_strides, const int32_t* zs_strides,
+                                       const gemq_stacked_t* w,
                                        void* y, int tokens, int N, int K, int group_size,
                                        void* workspace, size_t workspace_bytes, gemq_stream_t stream) {
-  if (!x || !indices || !wq || !scales || !zeros || !nbits || !wq_strides || !zs_strides || !y || A <= 0 ||
-      tokens <= 0 || N <= 0 || K <= 0 || group_size <= 0)
+  if (!x || !indices || !stacked_ok(w) || !w->zs_strides || !y || A <= 0 || tokens <= 0 || N <= 0 || K <= 0 ||
+      group_size <= 0)
     return GEMQ_ERR_BAD_ARG;
   if (A > kMaxJobs) return GEMQ_ERR_BAD_SHAPE;
   GemvParams P = {};
@@ -834,16 +835,10 @@ extern "C" int gemq_dequant_group_gemv(const void* x, int ldx, const int64_t* in
   P.T = tokens;
   for (int a = 0; a < A; ++a) {
     GemvJob& J = P.jobs[a];
-    J.wq = reinterpret_cast<const uint32_t*>(wq);
-    J.scales = static_cast<const __half*>(scales);
-    J.zeros = static_cast<const __half*>(zeros);
-    J.nbits = nbits;
-    J.wq_strides = wq_strides;
-    J.zs_strides = zs_strides;
-    J.idx = reinterpret_cast<const long long*>(indices) + a;
+    job_from_stacked(J, w, indices + a, N, K);
     J.xa = static_cast<const __half*>(x);
     J.y = static_cast<__half*>(y) + static_cast<size_t>(a) * tokens * N;
-    J.N = N; J.K = K; J.ldx = ldx; J.ldy = N;
+    J.ldx = ldx; J.ldy = N;
   }
   return run_gemv_jobs(P, false, group_size, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -22,6 +22,8 @@ constexpr int kSliceGroups = 8;           // k-slice of a CTA: 8 groups (1/2/4-b
 constexpr int kSliceGroupsB3 = 10;        //                   10 groups (3-bit: two 640-wide spans)
 constexpr int kRing = 8;                  // 128-bit weight loads in flight per lane
 constexpr int kMaxCounters = 8192;        // arrival counters at the head of the workspace
+constexpr int kMaxFamilies = 4;           // distinct (wq, scales, zeros) tensor triples per launch
+constexpr int kMaxMaps = 3 * kMaxFamilies;
 
 struct GemvJob {
   const uint32_t* wq;      // stacked (or single) packed words
@@ -41,6 +43,9 @@ struct GemvJob {
   int col_base;            // first column of this job inside a partial row
   int tile_base;           // first blockIdx.x of this job
   int chunk_base;          // first arrival counter of this job (shared by the jobs of a finish group)
+  int map_base;            // persistent kernel: index of this job's wq tensor map (+1 scales, +2 zeros)
+  long long wq_rows;       // host: rows of the wq tensor (tensor-map extent)
+  long long zs_rows;       // host: rows of the scales / zeros tensors
 };
 
 // How a finished column chunk is turned into outputs (persistent kernel).
@@ -49,7 +54,8 @@ enum { kEpiStore = 0,   // y = fp16(sum), each job on its own
        kEpiCombine = 2  // all jobs: weighted top-k combine (+ unit-weight shared experts)
 };
 
-struct GemvParams {
+struct alignas(64) GemvParams {
+  CUtensorMap maps[kMaxMaps];  // persistent kernel: tiled TMA descriptors of the weight / metadata tensors
   GemvJob jobs[kMaxJobs];
   int n_jobs;
   int T;           // activation rows

@@ -6,9 +6,11 @@
 // chunk-major, k-slice-minor and dealt to the CTAs in contiguous, byte-balanced ranges, so
 // a CTA usually owns all slices of a chunk and keeps the running sums on chip.  Inside a
 // CTA four roles run concurrently:
-//   * a producer warp streams the units into a 4-stage shared-memory ring with
-//     cp.async.bulk (one 512-byte copy per word row, mbarrier transaction counts): about
-//     130 KB per SM are in flight whatever the other warps are doing;
+//   * a producer warp streams the units into a 4-stage shared-memory ring with tiled TMA
+//     (cp.async.bulk.tensor.2d on the [word rows, N] tensors as they are: four 128B-swizzled
+//     boxes of 64 rows x 32 columns plus 4-row boxes of scales and offsets per unit,
+//     completion through mbarrier transaction counts): about 130 KB per SM are in flight
+//     whatever the other warps are doing;
 //   * a table warp turns the activation slice of each unit into the pre-scaled fp16
 //     operand table of that stage (one power-of-two scale and one sum per group);
 //   * sixteen consumer warps (4 column strips x 4 row quarters) run the in-place
@@ -20,6 +22,10 @@
 //     slots in order and runs the epilogue).  Global-memory latency of this protocol never
 //     stalls the consumers.
 // Every wait is bounded: on expiry the kernel records an error code and keeps going.
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "gemv.cuh"
 
 namespace gemq {
@@ -33,15 +39,28 @@ constexpr int kSThreads = 32 * kSWarps;
 constexpr int kSStages = 4;
 constexpr int kRedSlots = 4;
 constexpr int kUnitRows = 64;
-constexpr int kRowPitch = 544;  // 512 B of words + 32 B pad: conflict-free 128-bit reads across 4 rows
+constexpr int kStripBytes = kUnitRows * 128;  // one TMA box: 64 word rows x 32 columns, 128B-swizzled
 constexpr int kMaxUnitGroups = 16;
 constexpr int kSpinLimit = 1 << 18;
 constexpr int kErrSlot = kMaxCounters - 1;  // last counter word holds the error code
 
+#ifdef GEMQ_STREAM_TRACE
+// Development aid: nanosecond stamps of one CTA's roles (compiled out of the product build).
+__device__ unsigned long long g_trace[8][256];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define TRACE(row, i) do { if (blockIdx.x == 70 && (threadIdx.x & 31) == 0 && (i) < 256) g_trace[row][i] = gtime(); } while (0)
+#else
+#define TRACE(row, i) do { } while (0)
+#endif
+
 enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrRedFullWait = 3, kErrRedEmptyWait = 4 };
 
 struct StageBuf {
-  alignas(16) unsigned char words[kUnitRows * kRowPitch];
+  alignas(1024) unsigned char words[4 * kStripBytes];
   alignas(16) __half scales[kMaxUnitGroups][128];
   alignas(16) __half zeros[kMaxUnitGroups][128];
   alignas(16) uint32_t tab[1024];   // 1/2/4-bit: [64 rows][eps halves]; 3-bit: [2 variants][64 rows][16 halves]
@@ -50,9 +69,8 @@ struct StageBuf {
 };
 
 struct JobInfo {
-  const uint32_t* wq;
-  const __half* scales;
-  const __half* zeros;
+  int wq_row0, zs_row0;  // first row of the job's expert inside the stacked tensors
+  int map_base;
   int bits, slices, nch, groups_per_unit, ngroups, kw;
 };
 
@@ -109,11 +127,14 @@ __device__ __forceinline__ void mbar_wait(unsigned long long* bar, uint32_t pari
     if (mbar_try_wait(bar, parity)) return;
   atomicExch(err, code);
 }
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
+// Tiled TMA load of one box at element coordinates (x = column, y = row); x * element size
+// must be a multiple of 16 bytes (it is: columns come in multiples of 32).
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
 }
 
 __device__ __forceinline__ void mma16816s(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -168,12 +189,15 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P) {
   unsigned n_units = 0, unit_cost = 1;
   if (lane < P.n_jobs) {
     const GemvJob& J = P.jobs[lane];
-    const ResolvedJob R = resolve_job(J, kGroup);
+    const int e = J.idx ? static_cast<int>(*J.idx) : 0;
+    const int bits = J.nbits ? J.nbits[e] : J.fixed_bits;
     JobInfo I;
-    I.wq = R.wq; I.scales = R.scales; I.zeros = R.zeros;
-    I.bits = R.bits < 1 ? 1 : (R.bits > 4 ? 4 : R.bits);
-    I.groups_per_unit = unit_groups(I.bits);
     I.ngroups = J.K / kGroup;
+    I.wq_row0 = J.wq_strides ? J.wq_strides[e] / J.N : 0;
+    I.zs_row0 = J.zs_strides ? J.zs_strides[e] / J.N : e * I.ngroups;
+    I.map_base = J.map_base;
+    I.bits = bits < 1 ? 1 : (bits > 4 ? 4 : bits);
+    I.groups_per_unit = unit_groups(I.bits);
     I.slices = cdiv(I.ngroups, I.groups_per_unit);
     I.nch = cdiv(J.N, 128);
     I.kw = cdiv(J.K, 32 / I.bits);
@@ -226,17 +250,19 @@ __device__ void producer_role(StreamSmem& S, const GemvParams& P, int* err) {
       const uint32_t par = (it / kSStages) & 1;
       StageBuf& B = S.stage[st];
       mbar_wait(&S.empty[st], par ^ 1, err, kErrEmptyWait);
-      const uint32_t row_bytes = U.ncols * 4, meta_bytes = U.ncols * 2;
-      if (lane == 0) mbar_arrive_expect_tx(&S.full[st], U.nrows * row_bytes + 2 * U.ng * meta_bytes);
+      TRACE(0, it);
+      const int nstrips = U.ncols / 32, nmeta = (U.ng + 3) / 4;
+      if (lane == 0) mbar_arrive_expect_tx(&S.full[st], nstrips * kStripBytes + 2 * nmeta * 1024);
       __syncwarp();
-      const uint32_t* src = I.wq + static_cast<size_t>(U.wr0) * J.N + U.n0;
-      for (int r = lane; r < U.nrows; r += 32)
-        bulk_g2s(B.words + r * kRowPitch, src + static_cast<size_t>(r) * J.N, row_bytes, &S.full[st]);
-      for (int gi = lane; gi < 2 * U.ng; gi += 32) {
-        const int gq = gi >> 1;
-        const __half* msrc = ((gi & 1) ? I.zeros : I.scales) + static_cast<size_t>(U.g0 + gq) * J.N + U.n0;
-        bulk_g2s((gi & 1) ? B.zeros[gq] : B.scales[gq], msrc, meta_bytes, &S.full[st]);
+      if (lane < nstrips) {
+        tma_load_2d(B.words + lane * kStripBytes, &P.maps[I.map_base], U.n0 + 32 * lane, I.wq_row0 + U.wr0,
+                    &S.full[st]);
+      } else if (lane >= 4 && lane < 4 + 2 * nmeta) {
+        const int t = (lane - 4) & 1, q = (lane - 4) >> 1;
+        tma_load_2d(t ? static_cast<void*>(B.zeros[4 * q]) : static_cast<void*>(B.scales[4 * q]),
+                    &P.maps[I.map_base + 1 + t], U.n0, I.zs_row0 + U.g0 + 4 * q, &S.full[st]);
       }
+      TRACE(1, it);
     }
   }
 }
@@ -369,6 +395,7 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err) {
       make_unit(J, I, Pt.job, sl, Pt.chunk, U);
       const int st = it % kSStages;
       mbar_wait(&S.empty[st], ((it / kSStages) & 1) ^ 1, err, kErrEmptyWait);
+      TRACE(2, it);
       StageBuf& T = S.stage[st];
       if (U.bits == 1) build_table_pow2<1, XF32>(T, J.xa, U);
       else if (U.bits == 2) build_table_pow2<2, XF32>(T, J.xa, U);
@@ -376,6 +403,7 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err) {
       else build_table_pow2<4, XF32>(T, J.xa, U);
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.full[st]);
+      TRACE(3, it);
     }
   }
 }
@@ -411,21 +439,31 @@ __device__ __forceinline__ void apply_group(const StageBuf& Sg, int gu, int col,
 }
 
 // Rows [16*kp, 16*kp+16) of the unit, columns 32*cw + 4*g .. +3; adds into vs.
+// Word (row, 16-byte chunk ch) of column strip cw inside the 128B-swizzled box.
+__device__ __forceinline__ const uint4* strip_word(const StageBuf& Sg, int cw, int row, int ch) {
+  return reinterpret_cast<const uint4*>(Sg.words + cw * kStripBytes + row * 128 + ((ch ^ (row & 7)) << 4));
+}
+
+// 16-byte chunk of the strip (= 4 output columns) read by the lanes of MMA row pair g.  The
+// two row pairs of a quarter warp must differ in the chunk bit the swizzle does not cover:
+// bit 2 for the 1/2/4-bit access pattern (rows r+c), bit 0 for the 3-bit one (rows r+2c).
+__device__ __forceinline__ int lane_chunk(int bits, int g) { return bits == 3 ? g : ((g >> 1) | ((g & 1) << 2)); }
+
 template <int B>
 __device__ __forceinline__ void consume_pow2(const StageBuf& Sg, const uint32_t* zero_row, const Unit& U, int cw,
                                              int kp, float (&vs)[2][4]) {
   using F = SFmt<B>;
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int ch = lane_chunk(B, g);
   float acc[2][4];
 #pragma unroll
   for (int s = 0; s < 2; ++s)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[s][e] = 0.f;
-  const unsigned char* wbase = Sg.words + (16 * kp + c) * kRowPitch + (32 * cw + 4 * g) * 4;
   uint4 w4[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
-    if (16 * kp + 4 * i < U.nrows) w4[i] = *reinterpret_cast<const uint4*>(wbase + i * 4 * kRowPitch);
+    if (16 * kp + 4 * i < U.nrows) w4[i] = *strip_word(Sg, cw, 16 * kp + 4 * i + c, ch);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     if (16 * kp + 4 * i < U.nrows) {
@@ -452,7 +490,7 @@ __device__ __forceinline__ void consume_pow2(const StageBuf& Sg, const uint32_t*
   for (int p = 0; p < 2; ++p) {
     const int d = 2 * c + p;
     const int gu = kp * GPQ + d;
-    if (d < GPQ && gu < U.ng) apply_group(Sg, gu, 32 * cw + 4 * g, Sg.xsum[gu], acc, p, vs);
+    if (d < GPQ && gu < U.ng) apply_group(Sg, gu, 32 * cw + 4 * ch, Sg.xsum[gu], acc, p, vs);
   }
 }
 
@@ -482,7 +520,7 @@ __device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* z
       for (int r = 0; r < 2; ++r) {
         const int row = 16 * kp + 8 * i + 2 * c + r;
         uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (row < U.nrows) w = *reinterpret_cast<const uint4*>(Sg.words + row * kRowPitch + (32 * cw + 4 * g) * 4);
+        if (row < U.nrows) w = *strip_word(Sg, cw, row, g);
         mw[r][0] = S3Fmt::merge(w.x); mw[r][1] = S3Fmt::merge(w.y);
         mw[r][2] = S3Fmt::merge(w.z); mw[r][3] = S3Fmt::merge(w.w);
         const int d0 = (row * 10) >> 7;
@@ -510,7 +548,7 @@ __device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* z
   for (int p = 0; p < 2; ++p) {
     const int d = 2 * c + p;  // unit-local group carried by C column d
     // groups are not aligned to the row quarters: the offset term is added once, by quarter 0
-    if (d < 5 && d < U.ng) apply_group(Sg, d, 32 * cw + 4 * g, kp == 0 ? Sg.xsum[d] : 0.f, acc, p, vs);
+    if (d < 5 && d < U.ng) apply_group(Sg, d, 32 * cw + 4 * g, kp == 0 ? Sg.xsum[d] : 0.f, acc, p, vs);  // chunk = g
   }
 }
 
@@ -536,6 +574,7 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
       const int st = it % kSStages;
       const StageBuf& B = S.stage[st];
       mbar_wait(&S.full[st], (it / kSStages) & 1, err, kErrFullWait);
+      if (warp == 0) TRACE(4, it);
       if (32 * cw < U.ncols && 16 * kp < U.nrows) {
         if (U.bits == 1) consume_pow2<1>(B, S.zero_row, U, cw, kp, vs);
         else if (U.bits == 2) consume_pow2<2>(B, S.zero_row, U, cw, kp, vs);
@@ -544,6 +583,7 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.empty[st]);
+      if (warp == 0) TRACE(5, it);
     }
     // end of the part: sum the 8 MMA columns (= groups) and hand the strip to the finisher
 #pragma unroll
@@ -559,7 +599,8 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
     const int slot = pc % kRedSlots;
     mbar_wait(&S.redempty[slot], ((pc / kRedSlots) & 1) ^ 1, err, kErrRedEmptyWait);
     if (c == 0)
-      *reinterpret_cast<float4*>(&S.red[slot][kp][32 * cw + 4 * g]) = make_float4(vs[0][0], vs[0][2], vs[1][0], vs[1][2]);
+      *reinterpret_cast<float4*>(&S.red[slot][kp][32 * cw + 4 * lane_chunk(I.bits, g)]) =
+          make_float4(vs[0][0], vs[0][2], vs[1][0], vs[1][2]);
     __syncwarp();
     if (lane == 0) mbar_arrive(&S.redfull[slot]);
     ++pc;
@@ -637,6 +678,7 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
     const JobInfo& I = S.info[Pt.job];
     const int slot = pc % kRedSlots;
     mbar_wait(&S.redfull[slot], (pc / kRedSlots) & 1, err, kErrRedFullWait);
+    TRACE(6, pc);
     float4 r = *reinterpret_cast<const float4*>(&S.red[slot][0][4 * lane]);
 #pragma unroll
     for (int q = 1; q < 4; ++q) {
@@ -684,8 +726,9 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
 
 template <bool XF32>
 __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_constant__ GemvParams P) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  StreamSmem& S = *reinterpret_cast<StreamSmem*>(smem_raw);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  StreamSmem& S = *reinterpret_cast<StreamSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   int* err = P.counters + kErrSlot;
   if (threadIdx.x == 0) {
@@ -702,12 +745,15 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   if (threadIdx.x < 16) S.zero_row[threadIdx.x] = 0u;
   if (warp == 0) make_plan(S, P);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) TRACE(7, 0);
   __syncthreads();
+  if (warp == 1) TRACE(7, 1);
   if (warp < kSConsumers) consumer_role(S, P, err);
   else if (warp == kWarpProducer) producer_role(S, P, err);
   else if (warp == kWarpTable) table_role<XF32>(S, P, err);
   else finisher_role(S, P, err);
   __syncthreads();
+  if (warp == 1) TRACE(7, 2);
 }
 
 // h[i] = silu(x1[i]) * x3[i] in fp32 (gemq/triton_kernels/fused_dequant_bmm.py:237-239)
@@ -717,6 +763,63 @@ __global__ void silu_mul_kernel(const __half* __restrict__ x1, const __half* __r
 }
 
 // ---- host ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  long long rows;
+  int N, weights, dev;
+  bool operator<(const MapKey& o) const {
+    return std::tie(base, rows, N, weights, dev) < std::tie(o.base, o.rows, o.N, o.weights, o.dev);
+  }
+};
+
+// Descriptor of a row-major [rows, N] tensor: uint32 words with 64 x 32 boxes (128B swizzle)
+// or fp16 metadata with 4 x 128 boxes.  Cached: encoding costs a few microseconds of host time.
+static bool tensor_map(CUtensorMap* out, const void* base, int N, long long rows, bool weights) {
+  static std::mutex mu;
+  static std::map<MapKey, CUtensorMap> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const MapKey key{base, rows, N, weights ? 1 : 0, dev};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * (weights ? 4u : 2u)};
+  const cuuint32_t box[2] = {weights ? 32u : 128u, weights ? static_cast<cuuint32_t>(kUnitRows) : 4u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUtensorMap m;
+  const CUresult r = enc(&m, weights ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         weights ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return true;
+}
+
 static int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -734,7 +837,7 @@ static int launch_stream_t(GemvParams& P, cudaStream_t stream, int units_bound) 
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  const size_t smem = sizeof(StreamSmem);
+  const size_t smem = sizeof(StreamSmem) + 1024;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(gemv_stream_kernel<XF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
@@ -757,9 +860,22 @@ int silu_mul_f32(const __half* x1, const __half* x3, float* h, int n, cudaStream
 // aligned.  P.epi / P.x_f32 select epilogue and activation type; kEpiUpPair expects the
 // jobs in (gate, up) pairs.
 int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* counters, cudaStream_t stream) {
-  int cols = 0, chunks = 0, max_slices = 0, units = 0;
+  int cols = 0, chunks = 0, max_slices = 0, units = 0, families = 0;
   for (int i = 0; i < P.n_jobs; ++i) {
     GemvJob& J = P.jobs[i];
+    // tensor maps: jobs reading the same (wq, scales, zeros) tensors share one family
+    J.map_base = -1;
+    for (int k = 0; k < i; ++k)
+      if (P.jobs[k].wq == J.wq && P.jobs[k].scales == J.scales && P.jobs[k].zeros == J.zeros && P.jobs[k].N == J.N)
+        J.map_base = P.jobs[k].map_base;
+    if (J.map_base < 0) {
+      if (families == kMaxFamilies) return GEMQ_ERR_BAD_SHAPE;
+      J.map_base = 3 * families++;
+      if (!tensor_map(&P.maps[J.map_base], J.wq, J.N, J.wq_rows, true) ||
+          !tensor_map(&P.maps[J.map_base + 1], J.scales, J.N, J.zs_rows, false) ||
+          !tensor_map(&P.maps[J.map_base + 2], J.zeros, J.N, J.zs_rows, false))
+        return GEMQ_ERR_LAUNCH;
+    }
     const int nch = cdiv(J.N, 128);
     J.col_base = cols;
     J.tile_base = 0;
@@ -791,3 +907,9 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
 }
 
 }  // namespace gemq
+
+#ifdef GEMQ_STREAM_TRACE
+extern "C" int gemq_debug_read_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, gemq::g_trace, sizeof(gemq::g_trace)) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -40,6 +40,8 @@ static void stacked_job(GemvJob& J, const gemq_stacked_t& W, const int64_t* idx_
   J.wq_strides = W.wq_strides;
   J.zs_strides = W.zs_strides;
   J.idx = reinterpret_cast<const long long*>(idx_slot);
+  J.wq_rows = W.wq_rows;
+  J.zs_rows = W.zs_rows;
   J.N = N;
   J.K = K;
 }
@@ -49,6 +51,8 @@ static void single_job(GemvJob& J, const gemq_single_t& W, int N, int K) {
   J.scales = static_cast<const __half*>(W.scales);
   J.zeros = static_cast<const __half*>(W.zeros);
   J.fixed_bits = W.nbits;
+  J.wq_rows = cdiv(K, 32 / (W.nbits >= 1 && W.nbits <= 4 ? W.nbits : 4));
+  J.zs_rows = K / kGroup;
   J.N = N;
   J.K = K;
 }

@@ -4,7 +4,7 @@
 
 namespace gemq {
 
-constexpr int kRouteThreads = 256;
+constexpr int kRouteThreads = 1024;
 constexpr int kRouteMaxExperts = 256;
 constexpr int kRouteMaxTopK = 16;
 
@@ -41,24 +41,51 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restric
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* xt = x + static_cast<size_t>(t) * D;
-  const bool vec = (D % 8 == 0) && ((reinterpret_cast<uintptr_t>(xt) & 15u) == 0) &&
+  // An expert row is cut into `parts` segments so that all 32 warps pull on the gate matrix at
+  // once and every lane has all its 128-bit loads in flight before the first multiply.
+  __shared__ float part_sum[kRouteMaxExperts][8];
+  constexpr int NW = kRouteThreads / 32;
+  int parts = E >= NW ? 1 : NW / E;
+  parts = parts > 8 ? 8 : parts;
+  while (parts > 1 && (D % (parts * 256)) != 0) parts >>= 1;
+  const bool vec = (D % 256 == 0) && ((reinterpret_cast<uintptr_t>(xt) & 15u) == 0) &&
                    ((reinterpret_cast<uintptr_t>(gate) & 15u) == 0);
-  for (int e = warp; e < E; e += kRouteThreads / 32) {
-    const T* ge = gate + static_cast<size_t>(e) * D;
+  if (!vec) parts = 1;
+  const int seg = D / parts;
+  for (int task = warp; task < E * parts; task += NW) {
+    const int e = task / parts, sg = task - e * parts;
+    const T* ge = gate + static_cast<size_t>(e) * D + static_cast<size_t>(sg) * seg;
+    const T* xs = xt + static_cast<size_t>(sg) * seg;
     float s = 0.f;
     if (vec) {
-      for (int k = lane * 8; k < D; k += 256)
-        s += dot8<T>(*reinterpret_cast<const uint4*>(xt + k), *reinterpret_cast<const uint4*>(ge + k));
+      for (int k0 = 0; k0 < seg; k0 += 4 * 256) {
+        uint4 gq[4], xq[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int k = k0 + (i * 32 + lane) * 8;
+          if (k < seg) {
+            gq[i] = *reinterpret_cast<const uint4*>(ge + k);
+            xq[i] = *reinterpret_cast<const uint4*>(xs + k);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (k0 + (i * 32 + lane) * 8 < seg) s += dot8<T>(xq[i], gq[i]);
+      }
     } else {
-      for (int k = lane; k < D; k += 32) s = fmaf(Act<T>::to_f(xt[k]), Act<T>::to_f(ge[k]), s);
+      for (int k = lane; k < seg; k += 32) s = fmaf(Act<T>::to_f(xs[k]), Act<T>::to_f(ge[k]), s);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) {
-      if (mode != 2) s = Act<T>::to_f(Act<T>::from_f(s));
-      logit[e] = s;
-      if (logits_out) logits_out[static_cast<size_t>(t) * E + e] = s;
-    }
+    if (lane == 0) part_sum[e][sg] = s;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += kRouteThreads) {
+    float s = 0.f;
+    for (int q = 0; q < parts; ++q) s += part_sum[e][q];
+    if (mode != 2) s = Act<T>::to_f(Act<T>::from_f(s));
+    logit[e] = s;
+    if (logits_out) logits_out[static_cast<size_t>(t) * E + e] = s;
   }
   __syncthreads();
   if (warp != 0) return;

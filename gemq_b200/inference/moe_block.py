@@ -68,8 +68,8 @@ class _QuantFusedMoEBase(nn.Module):
         self._nbits_host = [int(l.W_nbits) for l in experts_w1]
 
     def _stacked_struct(self, name: str) -> _capi.Stacked:
-        g = lambda s: getattr(self, f"{name}_{s}").data_ptr()
-        return _capi.Stacked(g("wq"), g("scales"), g("zeros"), g("nbits"), g("wq_strides"), g("zs_strides"))
+        g = lambda s: getattr(self, f"{name}_{s}")
+        return _capi.stacked(g("wq"), g("scales"), g("zeros"), g("nbits"), g("wq_strides"), g("zs_strides"))
 
     def _single_struct(self, name: str) -> _capi.Single:
         g = lambda s: getattr(self, f"shared_{name}_{s}").data_ptr()

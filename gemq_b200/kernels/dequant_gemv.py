@@ -1,6 +1,8 @@
 """Dequant-fused GEMV; same call signatures as gemq/triton_kernels/dequant_gemv.py."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 from torch import Tensor
 
@@ -46,9 +48,10 @@ def dequant_sel_splitk_gemv(x: Tensor, idx: Tensor, w_q: Tensor, scales: Tensor,
     x = x.contiguous()
     out = torch.empty((1, N), dtype=torch.float16, device=dev)
     ws = gemv_workspace(dev, N, K, 1)
+    scales, zeros = scales.contiguous(), zeros.contiguous()
+    st = _capi.stacked(w_q, scales, zeros, nbits, wq_strides)
     _capi.check("gemq_dequant_sel_gemv", _capi.lib.gemq_dequant_sel_gemv(
-        x.data_ptr(), idx.data_ptr(), w_q.data_ptr(), scales.contiguous().data_ptr(), zeros.contiguous().data_ptr(),
-        nbits.data_ptr(), wq_strides.data_ptr(), out.data_ptr(), N, K, group_size,
+        x.data_ptr(), idx.data_ptr(), ctypes.byref(st), out.data_ptr(), N, K, group_size,
         ws.data_ptr(), ws.numel(), stream_ptr(dev)))
     return out
 

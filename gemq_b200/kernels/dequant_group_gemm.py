@@ -2,6 +2,8 @@
 gemq/triton_kernels/dequant_group_gemm.py."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 from torch import Tensor
 
@@ -54,12 +56,12 @@ def dequant_group_gemm(x: Tensor, indices: Tensor, wq: Tensor, scales: Tensor, z
         for i in range(0, M, _ROW_BLOCK):
             m = min(_ROW_BLOCK, M - i)
             blocks.append((i, m, torch.empty((A, m, N), dtype=torch.float16, device=dev)))
+    st = _capi.stacked(wq, scales, zeros, nbits, wq_strides, zs_strides)
     for i, m, dst in blocks:
         ws = gemv_workspace(dev, A * N, K, m)
         xs = x[i:i + m]
         _capi.check("gemq_dequant_group_gemv", _capi.lib.gemq_dequant_group_gemv(
-            xs.data_ptr(), xs.stride(0), indices.data_ptr(), A, wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-            nbits.data_ptr(), wq_strides.data_ptr(), zs_strides.data_ptr(), dst.data_ptr(), m, N, K, G,
+            xs.data_ptr(), xs.stride(0), indices.data_ptr(), A, ctypes.byref(st), dst.data_ptr(), m, N, K, G,
             ws.data_ptr(), ws.numel(), stream_ptr(dev)))
         if dst is not out:
             out[:, i:i + m] = dst

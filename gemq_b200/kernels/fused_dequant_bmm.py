@@ -2,6 +2,8 @@
 signatures as gemq/triton_kernels/fused_dequant_bmm.py."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 from torch import Tensor
 
@@ -33,11 +35,11 @@ def fused_dequant_up_proj(x: Tensor, idx: Tensor, w1: Tensor, w3: Tensor,
     x1 = torch.empty((1, A * N), dtype=torch.float16, device=dev)
     x3 = torch.empty((1, A * N), dtype=torch.float16, device=dev)
     ws = gemv_workspace(dev, 2 * A * N, K, 1)
+    s1 = _capi.stacked(w1, w1_scales, w1_zeros, nbits, w_strides)
+    s3 = _capi.stacked(w3, w3_scales, w3_zeros, nbits, w_strides)
     _capi.check("gemq_fused_up_proj", _capi.lib.gemq_fused_up_proj(
-        x.data_ptr(), idx.data_ptr(), A, w1.data_ptr(), w3.data_ptr(),
-        w1_scales.data_ptr(), w1_zeros.data_ptr(), w3_scales.data_ptr(), w3_zeros.data_ptr(),
-        nbits.data_ptr(), w_strides.data_ptr(), x1.data_ptr(), x3.data_ptr(), N, K, group_size,
-        ws.data_ptr(), ws.numel(), stream_ptr(dev)))
+        x.data_ptr(), idx.data_ptr(), A, ctypes.byref(s1), ctypes.byref(s3), x1.data_ptr(), x3.data_ptr(),
+        N, K, group_size, ws.data_ptr(), ws.numel(), stream_ptr(dev)))
     return x1, x3
 
 
@@ -59,9 +61,9 @@ def fused_dequant_down_proj(x1: Tensor, x3: Tensor, idx: Tensor, w2: Tensor,
     x3 = x3.contiguous()
     x2 = torch.empty((1, A * N), dtype=torch.float16, device=dev)
     ws = gemv_workspace(dev, A * N, K, 1)
+    s2 = _capi.stacked(w2, w2_scales, w2_zeros, nbits, w_strides)
     _capi.check("gemq_fused_down_proj", _capi.lib.gemq_fused_down_proj(
-        x1.data_ptr(), x3.data_ptr(), idx.data_ptr(), A, w2.data_ptr(), w2_scales.data_ptr(), w2_zeros.data_ptr(),
-        nbits.data_ptr(), w_strides.data_ptr(), x2.data_ptr(), N, K, group_size,
+        x1.data_ptr(), x3.data_ptr(), idx.data_ptr(), A, ctypes.byref(s2), x2.data_ptr(), N, K, group_size,
         ws.data_ptr(), ws.numel(), stream_ptr(dev)))
     return x2
 

@@ -76,28 +76,37 @@ int gemq_dequant_gemv(const void* x, int ldx, const int32_t* wq, const void* sca
                       void* y, int ldy, int tokens, int N, int K, int nbits, int group_size,
                       void* workspace, size_t workspace_bytes, gemq_stream_t stream);
 
-/* dequant_sel_splitk_gemv_triton (dequant_gemv.py:225-270): expert idx[0] of stacked tensors. */
-int gemq_dequant_sel_gemv(const void* x, const int64_t* idx, const int32_t* wq, const void* scales,
-                          const void* zeros, const int32_t* nbits, const int32_t* wq_strides,
+/* Stacked experts of one projection (all pointers device memory): the tensors the reference's
+ * blocks build at gemq/inference/moe_block.py:111-142. */
+typedef struct {
+  const int32_t* wq;
+  const void* scales;
+  const void* zeros;
+  const int32_t* nbits;      /* [E] */
+  const int32_t* wq_strides; /* [E] int32 element offsets into wq */
+  const int32_t* zs_strides; /* [E] element offsets into scales/zeros, or NULL: expert e starts at row e*(K/G) */
+  int64_t wq_rows;           /* rows (dim 0) of the stacked wq tensor */
+  int64_t zs_rows;           /* rows (dim 0) of the stacked scales / zeros tensors */
+} gemq_stacked_t;
+
+/* dequant_sel_splitk_gemv_triton (dequant_gemv.py:225-270): expert idx[0] of stacked tensors
+ * (scale rows located as in :203, zs_strides is ignored). */
+int gemq_dequant_sel_gemv(const void* x, const int64_t* idx, const gemq_stacked_t* w,
                           void* y, int N, int K, int group_size,
                           void* workspace, size_t workspace_bytes, gemq_stream_t stream);
 
 /* fused_dequant_up_proj_triton (gemq/triton_kernels/fused_dequant_bmm.py:122-173):
- * x1[a*N+n], x3[a*N+n] = x @ deq(w1[idx[a]]), x @ deq(w3[idx[a]]); w1/w3 share nbits and
- * w_strides (:56-57). */
+ * x1[a*N+n], x3[a*N+n] = x @ deq(w1[idx[a]]), x @ deq(w3[idx[a]]); w3 uses w1's nbits and
+ * wq_strides (:56-57,80,98) and both use e*(K/G) scale rows (:62). */
 int gemq_fused_up_proj(const void* x, const int64_t* idx, int A,
-                       const int32_t* w1, const int32_t* w3,
-                       const void* w1_scales, const void* w1_zeros,
-                       const void* w3_scales, const void* w3_zeros,
-                       const int32_t* nbits, const int32_t* w_strides,
+                       const gemq_stacked_t* w1, const gemq_stacked_t* w3,
                        void* x1, void* x3, int N, int K, int group_size,
                        void* workspace, size_t workspace_bytes, gemq_stream_t stream);
 
 /* fused_dequant_down_proj_triton (fused_dequant_bmm.py:264-312):
  * x2[a*N+n] = (silu(x1[a*K+k]) * x3[a*K+k]) @ deq(w2[idx[a]]). */
 int gemq_fused_down_proj(const void* x1, const void* x3, const int64_t* idx, int A,
-                         const int32_t* w2, const void* w2_scales, const void* w2_zeros,
-                         const int32_t* nbits, const int32_t* w_strides,
+                         const gemq_stacked_t* w2,
                          void* x2, int N, int K, int group_size,
                          void* workspace, size_t workspace_bytes, gemq_stream_t stream);
 
@@ -106,8 +115,7 @@ int gemq_fused_down_proj(const void* x1, const void* x3, const int64_t* idx, int
  * ldx), y fp16 [A, tokens, N] contiguous.  Per-expert scale offsets come from zs_strides
  * (:75,80-81); one group size for all experts. */
 int gemq_dequant_group_gemv(const void* x, int ldx, const int64_t* indices, int A,
-                            const int32_t* wq, const void* scales, const void* zeros,
-                            const int32_t* nbits, const int32_t* wq_strides, const int32_t* zs_strides,
+                            const gemq_stacked_t* w,
                             void* y, int tokens, int N, int K, int group_size,
                             void* workspace, size_t workspace_bytes, gemq_stream_t stream);
 
@@ -126,16 +134,6 @@ int gemq_moe_route(const void* x, const void* gate, int tokens, int D, int E, in
                    int64_t* idx, void* weights, float* logits, gemq_stream_t stream);
 
 /* ---- whole decode layer --------------------------------------------------------------- */
-
-/* One stacked projection family of a layer (all pointers device memory). */
-typedef struct {
-  const int32_t* wq;
-  const void* scales;
-  const void* zeros;
-  const int32_t* nbits;      /* [E] */
-  const int32_t* wq_strides; /* [E] */
-  const int32_t* zs_strides; /* [E] or NULL: expert e starts at row e*(K/G) */
-} gemq_stacked_t;
 
 /* One single (non-stacked) quantised matrix, e.g. a DeepSeek-V2 shared-expert projection. */
 typedef struct {
