@@ -438,7 +438,6 @@ __device__ __forceinline__ void apply_group(const StageBuf& Sg, int gu, int col,
   vs[1][2 + p] += fmaf(s23.y * fin, acc[1][2 + p], z23.y * xs);
 }
 
-// Rows [16*kp, 16*kp+16) of the unit, columns 32*cw + 4*g .. +3; adds into vs.
 // Word (row, 16-byte chunk ch) of column strip cw inside the 128B-swizzled box.
 __device__ __forceinline__ const uint4* strip_word(const StageBuf& Sg, int cw, int row, int ch) {
   return reinterpret_cast<const uint4*>(Sg.words + cw * kStripBytes + row * 128 + ((ch ^ (row & 7)) << 4));
@@ -449,48 +448,62 @@ __device__ __forceinline__ const uint4* strip_word(const StageBuf& Sg, int cw, i
 // bit 2 for the 1/2/4-bit access pattern (rows r+c), bit 0 for the 3-bit one (rows r+2c).
 __device__ __forceinline__ int lane_chunk(int bits, int g) { return bits == 3 ? g : ((g >> 1) | ((g & 1) << 2)); }
 
+// The sixteen consumer warps form two groups of eight that take alternate units, so that one
+// group's MMA phase overlaps the other's load / scale phases.  Inside a group a warp owns one
+// of 4 column strips and one of 2 row halves.
+constexpr int kConsumerGroups = 2;
+constexpr int kGroupWarps = kSConsumers / kConsumerGroups;
+constexpr int kRowsPerWarp = kUnitRows / (kGroupWarps / 4);  // 32
+
+// Rows [32*kp, 32*kp+32) of the unit, columns of strip cw chunk ch; adds into vs.
 template <int B>
-__device__ __forceinline__ void consume_pow2(const StageBuf& Sg, const uint32_t* zero_row, const Unit& U, int cw,
+__device__ __forceinline__ void consume_pow2(const StageBuf& Sg, const uint32_t* zero_row, int nrows, int ng, int cw,
                                              int kp, float (&vs)[2][4]) {
   using F = SFmt<B>;
+  constexpr int NI = kRowsPerWarp / 4;        // loop iterations: 4 word rows (one per c) each
+  constexpr int GPH = kRowsPerWarp / (4 * B); // groups inside this warp's rows = MMA columns in use
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int ch = lane_chunk(B, g);
+  const int r0 = kRowsPerWarp * kp;
   float acc[2][4];
 #pragma unroll
   for (int s = 0; s < 2; ++s)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[s][e] = 0.f;
-  uint4 w4[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-    if (16 * kp + 4 * i < U.nrows) w4[i] = *strip_word(Sg, cw, 16 * kp + 4 * i + c, ch);
+  for (int i0 = 0; i0 < NI; i0 += 4) {
+    uint4 w4[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (16 * kp + 4 * i < U.nrows) {
-      const int row = 16 * kp + 4 * i + c;
-      const uint32_t* bp = (g == i / B) ? Sg.tab + row * F::kPairs : zero_row;
-      uint32_t bf[F::kPairs];
+    for (int i = 0; i < 4; ++i)
+      if (r0 + 4 * (i0 + i) < nrows) w4[i] = *strip_word(Sg, cw, r0 + 4 * (i0 + i) + c, ch);
 #pragma unroll
-      for (int q4 = 0; q4 < F::kPairs / 4; ++q4) {
-        const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
-        bf[4 * q4 + 0] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
+    for (int i = 0; i < 4; ++i) {
+      if (r0 + 4 * (i0 + i) < nrows) {
+        const int row = r0 + 4 * (i0 + i) + c;
+        const uint32_t* bp = (g == (i0 + i) / B) ? Sg.tab + row * F::kPairs : zero_row;
+        uint32_t bf[F::kPairs];
+#pragma unroll
+        for (int q4 = 0; q4 < F::kPairs / 4; ++q4) {
+          const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
+          bf[4 * q4 + 0] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
+        }
+        const uint32_t wv[4] = {w4[i].x, w4[i].y, w4[i].z, w4[i].w};
+#pragma unroll
+        for (int m = 0; m < F::kMma; ++m)
+#pragma unroll
+          for (int s = 0; s < 2; ++s)
+            mma16816s(acc[s], F::operand(wv[2 * s], 2 * m), F::operand(wv[2 * s + 1], 2 * m),
+                      F::operand(wv[2 * s], 2 * m + 1), F::operand(wv[2 * s + 1], 2 * m + 1), bf[2 * m],
+                      bf[2 * m + 1]);
       }
-      const uint32_t wv[4] = {w4[i].x, w4[i].y, w4[i].z, w4[i].w};
-#pragma unroll
-      for (int m = 0; m < F::kMma; ++m)
-#pragma unroll
-        for (int s = 0; s < 2; ++s)
-          mma16816s(acc[s], F::operand(wv[2 * s], 2 * m), F::operand(wv[2 * s + 1], 2 * m),
-                    F::operand(wv[2 * s], 2 * m + 1), F::operand(wv[2 * s + 1], 2 * m + 1), bf[2 * m], bf[2 * m + 1]);
     }
   }
-  // C column 2c+p carries group 2c+p of this row quarter (4/B groups per quarter)
-  constexpr int GPQ = 4 / B;
+  // C column 2c+p carries group 2c+p of this row half
 #pragma unroll
   for (int p = 0; p < 2; ++p) {
     const int d = 2 * c + p;
-    const int gu = kp * GPQ + d;
-    if (d < GPQ && gu < U.ng) apply_group(Sg, gu, 32 * cw + 4 * ch, Sg.xsum[gu], acc, p, vs);
+    const int gu = kp * GPH + d;
+    if (d < GPH && gu < ng) apply_group(Sg, gu, 32 * cw + 4 * ch, Sg.xsum[gu], acc, p, vs);
   }
 }
 
@@ -503,24 +516,25 @@ struct S3Fmt {
   }
 };
 
-__device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* zero_row, const Unit& U, int cw,
+__device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* zero_row, int nrows, int ng, int cw,
                                            int kp, float (&vs)[2][4]) {
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int r0 = kRowsPerWarp * kp;
   float acc[2][4];
 #pragma unroll
   for (int s = 0; s < 2; ++s)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[s][e] = 0.f;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    if (16 * kp + 8 * i < U.nrows) {
+  for (int i = 0; i < kRowsPerWarp / 8; ++i) {
+    if (r0 + 8 * i < nrows) {
       uint32_t mw[2][4];
       uint32_t bf[10];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        const int row = 16 * kp + 8 * i + 2 * c + r;
+        const int row = r0 + 8 * i + 2 * c + r;
         uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (row < U.nrows) w = *strip_word(Sg, cw, row, g);
+        if (row < nrows) w = *strip_word(Sg, cw, row, g);
         mw[r][0] = S3Fmt::merge(w.x); mw[r][1] = S3Fmt::merge(w.y);
         mw[r][2] = S3Fmt::merge(w.z); mw[r][3] = S3Fmt::merge(w.w);
         const int d0 = (row * 10) >> 7;
@@ -547,14 +561,15 @@ __device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* z
 #pragma unroll
   for (int p = 0; p < 2; ++p) {
     const int d = 2 * c + p;  // unit-local group carried by C column d
-    // groups are not aligned to the row quarters: the offset term is added once, by quarter 0
-    if (d < 5 && d < U.ng) apply_group(Sg, d, 32 * cw + 4 * g, kp == 0 ? Sg.xsum[d] : 0.f, acc, p, vs);  // chunk = g
+    // groups are not aligned to the row halves: the offset term is added once, by half 0
+    if (d < 5 && d < ng) apply_group(Sg, d, 32 * cw + 4 * g, kp == 0 ? Sg.xsum[d] : 0.f, acc, p, vs);  // chunk = g
   }
 }
 
 __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int cw = warp & 3, kp = warp >> 2;
+  const int grp = warp / kGroupWarps, wl = warp % kGroupWarps;
+  const int cw = wl & 3, kp = wl >> 2;
   const int g = lane >> 2, c = lane & 3;
   PartWalk W;
   W.begin(S);
@@ -563,27 +578,29 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
   while (W.next(S, Pt)) {
     const GemvJob& J = P.jobs[Pt.job];
     const JobInfo& I = S.info[Pt.job];
+    const int ncols = min(128, J.N - Pt.chunk * 128);
+    const bool strip_on = 32 * cw < ncols;
     float vs[2][4];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
       for (int e = 0; e < 4; ++e) vs[s][e] = 0.f;
     for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
-      Unit U;
-      make_unit(J, I, Pt.job, sl, Pt.chunk, U);
+      if ((it & (kConsumerGroups - 1)) != grp) continue;  // the other group's unit
+      const int ng = min(I.groups_per_unit, I.ngroups - sl * I.groups_per_unit);
+      const int nrows = I.bits == 3 ? min(kUnitRows, I.kw - sl * kUnitRows) : ng * (4 * I.bits);
       const int st = it % kSStages;
       const StageBuf& B = S.stage[st];
       mbar_wait(&S.full[st], (it / kSStages) & 1, err, kErrFullWait);
-      if (warp == 0) TRACE(4, it);
-      if (32 * cw < U.ncols && 16 * kp < U.nrows) {
-        if (U.bits == 1) consume_pow2<1>(B, S.zero_row, U, cw, kp, vs);
-        else if (U.bits == 2) consume_pow2<2>(B, S.zero_row, U, cw, kp, vs);
-        else if (U.bits == 3) consume_b3(B, S.zero_row, U, cw, kp, vs);
-        else consume_pow2<4>(B, S.zero_row, U, cw, kp, vs);
+      if (wl == 0) TRACE(4 + grp, it >> 1);
+      if (strip_on && kRowsPerWarp * kp < nrows) {
+        if (I.bits == 1) consume_pow2<1>(B, S.zero_row, nrows, ng, cw, kp, vs);
+        else if (I.bits == 2) consume_pow2<2>(B, S.zero_row, nrows, ng, cw, kp, vs);
+        else if (I.bits == 3) consume_b3(B, S.zero_row, nrows, ng, cw, kp, vs);
+        else consume_pow2<4>(B, S.zero_row, nrows, ng, cw, kp, vs);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.empty[st]);
-      if (warp == 0) TRACE(5, it);
     }
     // end of the part: sum the 8 MMA columns (= groups) and hand the strip to the finisher
 #pragma unroll
@@ -599,7 +616,7 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
     const int slot = pc % kRedSlots;
     mbar_wait(&S.redempty[slot], ((pc / kRedSlots) & 1) ^ 1, err, kErrRedEmptyWait);
     if (c == 0)
-      *reinterpret_cast<float4*>(&S.red[slot][kp][32 * cw + 4 * lane_chunk(I.bits, g)]) =
+      *reinterpret_cast<float4*>(&S.red[slot][grp * 2 + kp][32 * cw + 4 * lane_chunk(I.bits, g)]) =
           make_float4(vs[0][0], vs[0][2], vs[1][0], vs[1][2]);
     __syncwarp();
     if (lane == 0) mbar_arrive(&S.redfull[slot]);
@@ -734,7 +751,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSStages; ++s) {
       mbar_init(&S.full[s], 2);  // producer (with the byte count) + table warp
-      mbar_init(&S.empty[s], kSConsumers);
+      mbar_init(&S.empty[s], kGroupWarps);  // only the group that owns the unit releases its stage
     }
     for (int s = 0; s < kRedSlots; ++s) {
       mbar_init(&S.redfull[s], kSConsumers);
