@@ -32,9 +32,10 @@ namespace gemq {
 
 constexpr int kSConsumers = 16;
 constexpr int kWarpProducer = kSConsumers;
-constexpr int kWarpTable = kSConsumers + 1;
-constexpr int kWarpFinisher = kSConsumers + 2;
-constexpr int kSWarps = kSConsumers + 3;
+constexpr int kWarpTable = kSConsumers + 1;   // first of kTableWarps table warps (they take alternate units)
+constexpr int kTableWarps = 2;
+constexpr int kWarpFinisher = kWarpTable + kTableWarps;
+constexpr int kSWarps = kWarpFinisher + 1;
 constexpr int kSThreads = 32 * kSWarps;
 constexpr int kSStages = 4;
 constexpr int kRedSlots = 4;
@@ -121,10 +122,15 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kSpinLimit polls, records `code` and returns.
-__device__ __forceinline__ void mbar_wait(unsigned long long* bar, uint32_t parity, int* err, int code) {
-  for (int i = 0; i < kSpinLimit; ++i)
+// Bounded wait: gives up after kSpinLimit polls, records `code` and returns.  A waiting warp
+// sleeps between polls so that it does not take issue slots from the warps that are working.
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, uint32_t parity, int* err, int code,
+                                          unsigned sleep_ns = 64) {
+  if (mbar_try_wait(bar, parity)) return;
+  for (int i = 0; i < kSpinLimit; ++i) {
+    __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return;
+  }
   atomicExch(err, code);
 }
 // Tiled TMA load of one box at element coordinates (x = column, y = row); x * element size
@@ -327,8 +333,10 @@ __device__ __forceinline__ void build_table_pow2(StageBuf& T, const void* x, con
     if (on) {
       uint32_t outw[PAIRS];
 #pragma unroll
+      const float fb = pow2i(c);
+#pragma unroll
       for (int q = 0; q < PAIRS; ++q) {
-        const float f = pow2i(c - B * (q % NPOS));
+        const float f = fb * (1.0f / static_cast<float>(1 << (B * (q % NPOS))));
         const __half2 h = __floats2half2_rn(xv[q] * f, xv[q + PAIRS] * f);
         outw[q] = *reinterpret_cast<const uint32_t*>(&h);
       }
@@ -381,7 +389,7 @@ __device__ __forceinline__ void build_table_b3(StageBuf& T, const void* x, const
 }
 
 template <bool XF32>
-__device__ void table_role(StreamSmem& S, const GemvParams& P, int* err) {
+__device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw) {
   const int lane = threadIdx.x & 31;
   PartWalk W;
   W.begin(S);
@@ -391,6 +399,7 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err) {
     const GemvJob& J = P.jobs[Pt.job];
     const JobInfo& I = S.info[Pt.job];
     for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
+      if (it % kTableWarps != tw) continue;  // a single warp is latency-bound at about one unit per microsecond
       Unit U;
       make_unit(J, I, Pt.job, sl, Pt.chunk, U);
       const int st = it % kSStages;
@@ -760,17 +769,29 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (threadIdx.x < 16) S.zero_row[threadIdx.x] = 0u;
+  if (warp == kWarpProducer && (threadIdx.x & 31) < kMaxMaps)  // descriptor fetch overlaps the plan
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&P.maps[threadIdx.x & 31])) : "memory");
+  // Let the next kernel of the stream start its own prologue as SMs free up, then wait until
+  // the previous kernel's results (expert ids, activations, zeroed workspace) are visible.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (warp == 0) make_plan(S, P);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 1) TRACE(7, 0);
   __syncthreads();
   if (warp == 1) TRACE(7, 1);
+#ifdef GEMQ_STREAM_TRACE
+  if (blockIdx.x == 70 && threadIdx.x == 32) g_trace[7][3] = clock64();
+#endif
   if (warp < kSConsumers) consumer_role(S, P, err);
   else if (warp == kWarpProducer) producer_role(S, P, err);
-  else if (warp == kWarpTable) table_role<XF32>(S, P, err);
+  else if (warp < kWarpFinisher) table_role<XF32>(S, P, err, warp - kWarpTable);
   else finisher_role(S, P, err);
   __syncthreads();
   if (warp == 1) TRACE(7, 2);
+#ifdef GEMQ_STREAM_TRACE
+  if (blockIdx.x == 70 && threadIdx.x == 32) g_trace[7][4] = clock64();
+#endif
 }
 
 // h[i] = silu(x1[i]) * x3[i] in fp32 (gemq/triton_kernels/fused_dequant_bmm.py:237-239)
@@ -864,7 +885,19 @@ static int launch_stream_t(GemvParams& P, cudaStream_t stream, int units_bound) 
   const int sms = sm_count();
   if (sms <= 0) return GEMQ_ERR_LAUNCH;
   const int grid = units_bound < sms ? units_bound : sms;
-  gemv_stream_kernel<XF32><<<grid, kSThreads, smem, stream>>>(P);
+  // Programmatic dependent launch: this grid may be scheduled while the previous kernel of the
+  // stream drains; everything that reads that kernel's results sits behind griddepcontrol.wait.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kSThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<XF32>, P) != cudaSuccess) return GEMQ_ERR_LAUNCH;
   return launch_status();
 }
 

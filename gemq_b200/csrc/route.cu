@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restric
                                                               long long* __restrict__ idx, T* __restrict__ weights,
                                                               float* __restrict__ logits_out) {
   __shared__ float logit[kRouteMaxExperts];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the previous kernel of the stream
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* xt = x + static_cast<size_t>(t) * D;
@@ -159,14 +161,24 @@ extern "C" int gemq_moe_route(const void* x, const void* gate, int tokens, int D
   if (!x || !gate || !idx || !weights || tokens <= 0 || D <= 0 || E <= 0 || A <= 0 || mode < 0 || mode > 2)
     return GEMQ_ERR_BAD_ARG;
   if (E > kRouteMaxExperts || A > kRouteMaxTopK || A > E) return GEMQ_ERR_BAD_SHAPE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tokens);
+  cfg.blockDim = dim3(kRouteThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
   if (x_is_bf16)
-    route_kernel<__nv_bfloat16><<<tokens, kRouteThreads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate), D, E, A, mode, renorm,
-        reinterpret_cast<long long*>(idx), static_cast<__nv_bfloat16*>(weights), logits);
+    e = cudaLaunchKernelEx(&cfg, route_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x),
+                           static_cast<const __nv_bfloat16*>(gate), D, E, A, mode, renorm,
+                           reinterpret_cast<long long*>(idx), static_cast<__nv_bfloat16*>(weights), logits);
   else
-    route_kernel<__half><<<tokens, kRouteThreads, 0, s>>>(
-        static_cast<const __half*>(x), static_cast<const __half*>(gate), D, E, A, mode, renorm,
-        reinterpret_cast<long long*>(idx), static_cast<__half*>(weights), logits);
+    e = cudaLaunchKernelEx(&cfg, route_kernel<__half>, static_cast<const __half*>(x),
+                           static_cast<const __half*>(gate), D, E, A, mode, renorm,
+                           reinterpret_cast<long long*>(idx), static_cast<__half*>(weights), logits);
+  if (e != cudaSuccess) return GEMQ_ERR_LAUNCH;
   return launch_status();
 }
