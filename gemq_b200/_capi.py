@@ -60,6 +60,10 @@ _SIGNATURES = {
     "gemq_dequant_group_gemv": (_I, [_P, _I, _P, _I, C.POINTER(Stacked), _P, _I, _I, _I, _I, _P, _Z, _P]),
     "gemq_moe_route": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
     "gemq_moe_decode_scratch_bytes": (_Z, [C.POINTER(MoeLayer)]),
+    "gemq_dequant_gemm_tc": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P]),
+    "gemq_moe_prefill_scratch_bytes": (_Z, [C.POINTER(MoeLayer), _I]),
+    "gemq_moe_prefill": (_I, [C.POINTER(MoeLayer), _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
+    "gemq_moe_prefill_error_word": (_P, [C.POINTER(MoeLayer), _I, _P]),
     "gemq_moe_decode": (_I, [C.POINTER(MoeLayer), _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
 }
 

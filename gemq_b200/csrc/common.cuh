@@ -37,6 +37,10 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
   return v;
 }
 
+// tma.cu
+bool tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, int inner, long long rows, int box_inner,
+                   int box_rows, bool swizzle128);
+
 __device__ __forceinline__ float pow2i(int e) {  // 2^e for e in [-126, 127]
   return __int_as_float((e + 127) << 23);
 }

@@ -22,11 +22,8 @@
 //     slots in order and runs the epilogue).  Global-memory latency of this protocol never
 //     stalls the consumers.
 // Every wait is bounded: on expiry the kernel records an error code and keeps going.
-#include <map>
-#include <mutex>
-#include <tuple>
-
 #include "gemv.cuh"
+#include "ptx.cuh"
 
 namespace gemq {
 
@@ -42,7 +39,6 @@ constexpr int kRedSlots = 4;
 constexpr int kUnitRows = 64;
 constexpr int kStripBytes = kUnitRows * 128;  // one TMA box: 64 word rows x 32 columns, 128B-swizzled
 constexpr int kMaxUnitGroups = 16;
-constexpr int kSpinLimit = 1 << 18;
 constexpr int kErrSlot = kMaxCounters - 1;  // last counter word holds the error code
 
 #ifdef GEMQ_STREAM_TRACE
@@ -98,50 +94,6 @@ struct Unit {
 struct Part {
   int job, chunk, sa, sb;
 };
-
-// ---- mbarrier / bulk-copy primitives -------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up after kSpinLimit polls, records `code` and returns.  A waiting warp
-// sleeps between polls so that it does not take issue slots from the warps that are working.
-__device__ __forceinline__ void mbar_wait(unsigned long long* bar, uint32_t parity, int* err, int code,
-                                          unsigned sleep_ns = 64) {
-  if (mbar_try_wait(bar, parity)) return;
-  for (int i = 0; i < kSpinLimit; ++i) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return;
-  }
-  atomicExch(err, code);
-}
-// Tiled TMA load of one box at element coordinates (x = column, y = row); x * element size
-// must be a multiple of 16 bytes (it is: columns come in multiples of 32).
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          smem_u32(dst)),
-      "l"(reinterpret_cast<unsigned long long>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
 
 __device__ __forceinline__ void mma16816s(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
@@ -801,61 +753,11 @@ __global__ void silu_mul_kernel(const __half* __restrict__ x1, const __half* __r
 }
 
 // ---- host ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-struct MapKey {
-  const void* base;
-  long long rows;
-  int N, weights, dev;
-  bool operator<(const MapKey& o) const {
-    return std::tie(base, rows, N, weights, dev) < std::tie(o.base, o.rows, o.N, o.weights, o.dev);
-  }
-};
-
 // Descriptor of a row-major [rows, N] tensor: uint32 words with 64 x 32 boxes (128B swizzle)
-// or fp16 metadata with 4 x 128 boxes.  Cached: encoding costs a few microseconds of host time.
+// or fp16 metadata with 4 x 128 boxes.
 static bool tensor_map(CUtensorMap* out, const void* base, int N, long long rows, bool weights) {
-  static std::mutex mu;
-  static std::map<MapKey, CUtensorMap> cache;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const MapKey key{base, rows, N, weights ? 1 : 0, dev};
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) {
-    *out = it->second;
-    return true;
-  }
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * (weights ? 4u : 2u)};
-  const cuuint32_t box[2] = {weights ? 32u : 128u, weights ? static_cast<cuuint32_t>(kUnitRows) : 4u};
-  const cuuint32_t estr[2] = {1u, 1u};
-  CUtensorMap m;
-  const CUresult r = enc(&m, weights ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
-                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         weights ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return false;
-  if (cache.size() > 4096) cache.clear();
-  cache[key] = m;
-  *out = m;
-  return true;
+  return weights ? tensor_map_2d(out, base, 4, N, rows, 32, kUnitRows, true)
+                 : tensor_map_2d(out, base, 2, N, rows, 128, 4, false);
 }
 
 static int sm_count() {

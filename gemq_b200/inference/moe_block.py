@@ -43,6 +43,7 @@ class _QuantFusedMoEBase(nn.Module):
         self.block_group_size = None
         self._layer = None       # ctypes struct handed to the library
         self._scratch = None
+        self._prefill_scratch = None
         self._nbits_host = None
 
     # -- construction ---------------------------------------------------------------
@@ -114,6 +115,43 @@ class _QuantFusedMoEBase(nn.Module):
             int(x.dtype == torch.bfloat16), idx.data_ptr(), w.data_ptr(), logits.data_ptr(), stream_ptr(dev)))
         return w, idx, logits
 
+    def _prefill_ok(self) -> bool:
+        D, Fd, G = self.hidden_dim, self.ffn_dim, self.block_group_size
+        ok = D % 128 == 0 and Fd % 128 == 0 and G % 64 == 0 and self.top_k <= 8 and self.num_experts <= 256
+        sf = self._layer.shared_ffn
+        return ok and (sf == 0 or (sf % 128 == 0 and self.shared_group_size % 64 == 0))
+
+    def _prefill(self, x: Tensor, route_mode: int, renorm: bool):
+        """``x [T, D]`` fp16/bf16 -> ``(out, weights, indices, logits)`` through the expert-sorted
+        tcgen05 grouped GEMM; no host synchronisation."""
+        dev = require_cuda(x)
+        x = x.contiguous()
+        T = x.shape[0]
+        bf = x.dtype == torch.bfloat16
+        nbytes = _capi.lib.gemq_moe_prefill_scratch_bytes(C.byref(self._layer), T)
+        if self._prefill_scratch is None or self._prefill_scratch.numel() < nbytes:
+            self._prefill_scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        out = torch.empty_like(x)
+        if bf:  # the library's router reads the fp16 gate of the layer: route here with a bf16 copy
+            w, idx, logits = self._route(x, route_mode, renorm)
+            do_route = 0
+        else:
+            idx = torch.empty((T, self.top_k), dtype=torch.int64, device=dev)
+            w = torch.empty((T, self.top_k), dtype=x.dtype, device=dev)
+            logits = torch.empty((T, self.num_experts), dtype=torch.float32, device=dev)
+            do_route = 1
+        sc = self._prefill_scratch
+        _capi.check("gemq_moe_prefill", _capi.lib.gemq_moe_prefill(
+            C.byref(self._layer), x.data_ptr(), out.data_ptr(), idx.data_ptr(), w.data_ptr(), logits.data_ptr(),
+            T, do_route, route_mode, int(bf), sc.data_ptr(), sc.numel(), stream_ptr(dev)))
+        return out, w, idx, logits
+
+    def prefill_error_code(self, tokens: int) -> int:
+        """Error word of the last prefill with this many tokens (0 = no bounded wait expired); syncs."""
+        p = _capi.lib.gemq_moe_prefill_error_word(C.byref(self._layer), tokens, self._prefill_scratch.data_ptr())
+        off = p - self._prefill_scratch.data_ptr()
+        return int(self._prefill_scratch[off:off + 4].view(torch.int32).item())
+
     def forward_single_expert(self, expert_idx: Tensor, hidden_states: Tensor) -> Tensor:
         """Expert FFN on ``[T, D]`` rows (gemq/inference/moe_block.py:146-163)."""
         x = hidden_states
@@ -173,6 +211,9 @@ class QuantFusedMixtralMoEBlock(_QuantFusedMoEBase):
         """gemq/inference/moe_block.py:165-198."""
         b, s, d = hidden_states.shape
         x = hidden_states.reshape(-1, d)
+        if self._prefill_ok() and x.dtype in (torch.float16, torch.bfloat16):
+            out, _, _, logits = self._prefill(x, ROUTE_FP32_SOFTMAX, True)
+            return out.reshape(b, s, d), logits.to(hidden_states.dtype)
         rw, sel, logits = self._route(x, ROUTE_FP32_SOFTMAX, True)
         out = self._experts_n_tokens(x, rw, sel)
         return out.reshape(b, s, d), logits.to(hidden_states.dtype)
@@ -254,6 +295,9 @@ class QuantFusedDeepseekV2MoEBlock(_QuantFusedMoEBase):
             xh = x if x.dtype == torch.float16 else x.to(torch.float16)
             out, _, _ = self._decode(xh.contiguous(), ROUTE_FP32)
             return out.to(hidden_states.dtype).reshape(b, s, d)
+        if self._prefill_ok() and x.dtype in (torch.float16, torch.bfloat16):
+            out, _, _, _ = self._prefill(x, ROUTE_FP32, bool(self.norm_topk_prob))
+            return out.reshape(b, s, d)
         rw, sel, _ = self._route(x, ROUTE_FP32, bool(self.norm_topk_prob))
         out = self._experts_n_tokens(x, rw, sel)
         xh = x if x.dtype == torch.float16 else x.to(torch.float16)

@@ -59,3 +59,21 @@ def check_kernel_form(wq, scales, zeros, K: int, N: int, nbits: int, group_size:
     for name, t in (("scales", scales), ("zeros", zeros)):
         require(t.dtype == torch.float16 and t.is_contiguous(), f"{name} must be contiguous float16")
         require(tuple(t.shape) == (K // group_size, N), f"{name} shape {tuple(t.shape)} != {(K // group_size, N)}")
+
+
+_err_words: dict = {}
+
+
+def error_word(dev: torch.device) -> torch.Tensor:
+    """One int32 per device that kernels with bounded waits set when a wait expires."""
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    t = _err_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _err_words[key] = t
+    return t
+
+
+def tc_gemm_ok(M: int, N: int, K: int, group_size: int) -> bool:
+    """Shapes the tcgen05 GEMM takes; smaller row counts stay on the decode kernel."""
+    return M >= 32 and N % 128 == 0 and K % 64 == 0 and group_size % 64 == 0 and K % group_size == 0

@@ -8,7 +8,7 @@ import torch
 from torch import Tensor
 
 from .. import _capi
-from ._runtime import gemv_workspace, require, require_cuda, stream_ptr
+from ._runtime import error_word, gemv_workspace, require, require_cuda, stream_ptr, tc_gemm_ok
 
 _ROW_BLOCK = 64
 _group_size_cache: dict = {}
@@ -49,6 +49,14 @@ def dequant_group_gemm(x: Tensor, indices: Tensor, wq: Tensor, scales: Tensor, z
     scales = scales.contiguous()
     zeros = zeros.contiguous()
     out = torch.empty((A, M, N), dtype=torch.float16, device=dev)
+    if tc_gemm_ok(M, N, K, G):
+        x = x.contiguous()
+        for g in range(A):
+            _capi.check("gemq_dequant_gemm_tc", _capi.lib.gemq_dequant_gemm_tc(
+                x.data_ptr(), indices[g:g + 1].data_ptr(), wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                nbits.data_ptr(), wq_strides.data_ptr(), zs_strides.data_ptr(), 0, out[g].data_ptr(), M, N, K, G, 0,
+                error_word(dev).data_ptr(), stream_ptr(dev)))
+        return out
     if M <= _ROW_BLOCK:
         blocks = [(0, M, out)]
     else:

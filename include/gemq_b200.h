@@ -173,6 +173,37 @@ int gemq_moe_decode(const gemq_moe_layer_t* layer, const void* x, void* out,
                     int64_t* idx, void* w, int tokens, int do_route, int route_mode,
                     void* scratch, size_t scratch_bytes, gemq_stream_t stream);
 
+/* ---- prefill: tcgen05 grouped GEMM ----------------------------------------------------------- */
+
+/* dequant_gemm_triton (gemq/triton_kernels/dequant_gemm.py:150-193) and one group of
+ * dequant_group_gemm_triton (dequant_group_gemm.py:155-202) on the tcgen05 tensor cores:
+ * y[M, N] = x[M, K] @ deq(W[e]), x and y contiguous fp16 (or bf16 when x_is_bf16; the
+ * de-quantised fp16 weights are then rounded to bf16).  `expert` = device pointer to the expert
+ * id (NULL: expert 0); nbits / wq_strides / zs_strides may be NULL for a single matrix with
+ * fixed_bits.  Needs N % 128 == 0, K % 64 == 0, group_size % 64 == 0.  `err` = one device int32
+ * that receives a non-zero code if a bounded wait inside the kernel expired. */
+int gemq_dequant_gemm_tc(const void* x, const int64_t* expert, const int32_t* wq, const void* scales,
+                         const void* zeros, const int32_t* nbits, const int32_t* wq_strides,
+                         const int32_t* zs_strides, int fixed_bits, void* y, int M, int N, int K,
+                         int group_size, int x_is_bf16, int32_t* err, gemq_stream_t stream);
+
+/* Device scratch of gemq_moe_prefill for `tokens` rows. */
+size_t gemq_moe_prefill_scratch_bytes(const gemq_moe_layer_t* layer, int tokens);
+
+/* forward_n_tokens of the quantised blocks (gemq/inference/moe_block.py:165-198, :448-486)
+ * without host synchronisation: route (when do_route), count / scan / scatter the (token, expert)
+ * pairs into expert-sorted rows, grouped gate/up GEMM with the SiLU*mul epilogue, grouped down
+ * GEMM scaled by the routing weight, per-token combine in expert order, shared experts.
+ * x, out: [tokens, D] fp16 or bf16; idx int64 [tokens, A]; w [tokens, A] in the activation dtype;
+ * logits fp32 [tokens, E] or NULL.  With do_route the gate of `layer` (fp16) is used, so bf16
+ * callers route first (gemq_moe_route) and pass do_route = 0. */
+int gemq_moe_prefill(const gemq_moe_layer_t* layer, const void* x, void* out, int64_t* idx, void* w,
+                     float* logits, int tokens, int do_route, int route_mode, int x_is_bf16,
+                     void* scratch, size_t scratch_bytes, gemq_stream_t stream);
+
+/* Device address of the error word gemq_moe_prefill writes in `scratch` (0 = every wait was met). */
+const int32_t* gemq_moe_prefill_error_word(const gemq_moe_layer_t* layer, int tokens, void* scratch);
+
 #ifdef __cplusplus
 }
 #endif

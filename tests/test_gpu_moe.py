@@ -119,3 +119,55 @@ def test_mixtral_config1_full_size_decode():
     check(out.view(1, -1), acc[None, :])
     out2, _ = blk(x)
     assert torch.equal(out, out2)
+
+
+def test_gemm_tc_vs_oracle():
+    """tcgen05 GEMM: single matrix, every bit-width, ragged last row tile."""
+    from gemq_b200.kernels import dequant_gemm
+    from gemq_b200.kernels._runtime import error_word
+    for b in (1, 2, 3, 4):
+        rng = np.random.default_rng(40 + b)
+        N, K, M = 256, 512, 200
+        lin = MF.draw_linear(rng, N, K, b)
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        y = dequant_gemm(t(x), t(lin["wq"]), t(lin["s"]), t(lin["z"]), b, 128)
+        assert int(error_word(y.device).item()) == 0
+        check(y, O.dequant_gemm(x, lin["wq"], lin["s"], lin["z"], b, 128))
+
+
+def test_mixtral_prefill_grouped_gemm():
+    layer = MF.make_layer("mixtral", D=256, Fd=512, E=4, A=2, bits=[4, 1, 3, 2], seed=6, gate_std=0.02)
+    blk = MF.gpu_block(layer)
+    assert blk._prefill_ok()
+    w1, w3, w2, _ = MF.oracle_parts(layer)
+    T = 300
+    x = torch.randn(T, 256, generator=torch.Generator().manual_seed(3)).half()
+    out, logits = blk(x.cuda().view(1, T, -1))
+    assert blk.prefill_error_code(T) == 0
+    _, gw, gi, _ = blk._prefill(x.cuda(), 1, True)
+    ref = O.moe_reference_fp32(x, gw.float().cpu(), gi.cpu(), w1, w3, w2)
+    check(out.view(T, -1), ref.numpy())
+    ref_out, ew, ei, ref_logits = O.moe_n_tokens(x, torch.from_numpy(layer["gate"]), 2, w1, w3, w2, "mixtral")
+    same = (gi.cpu().sort(dim=1).values == ei.sort(dim=1).values).all(dim=1)
+    assert same.float().mean() > 0.9
+    check(out.view(T, -1).float().cpu()[same], ref_out.float()[same].numpy())
+    out2, _ = blk(x.cuda().view(1, T, -1))
+    assert torch.equal(out, out2)
+
+
+def test_deepseek_prefill_with_shared_experts_bf16():
+    layer = MF.make_layer("deepseek", D=256, Fd=384, E=16, A=6, bits=[1, 2, 3, 4] * 4, seed=8, gate_std=1 / 16.0,
+                          n_shared=2)
+    blk = MF.gpu_block(layer)
+    assert blk._prefill_ok()
+    w1, w3, w2, sh = MF.oracle_parts(layer)
+    T = 70
+    x = torch.randn(T, 256, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16)
+    out = blk(x.cuda().view(1, T, -1)).view(T, -1)
+    assert out.dtype == torch.bfloat16 and blk.prefill_error_code(T) == 0
+    _, gw, gi, _ = blk._prefill(x.cuda(), 2, False)
+    ref = O.moe_reference_fp32(x.float(), gw.float().cpu(), gi.cpu(), w1, w3, w2, sh).numpy()
+    got = out.float().cpu().numpy()
+    # bf16 activations and bf16-rounded weights: 8 mantissa bits
+    assert rel_fro(got, ref) < 2e-2
