@@ -22,7 +22,8 @@ namespace gemq {
 
 constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 64;
 constexpr int kGemmStages = 3;
-constexpr int kGemmThreads = 192;  // 4 de-quantise/epilogue warps + TMA warp + MMA warp
+constexpr int kGemmProducerWarps = 8;
+constexpr int kGemmThreads = 32 * (kGemmProducerWarps + 2);  // 8 de-quantise/epilogue warps + TMA warp + MMA warp
 constexpr int kTileBytes = kGemmBM * kGemmBK * 2;  // 16 KB, A or B tile of one stage
 
 enum { kErrGemmAFull = 11, kErrGemmBFull = 12, kErrGemmEmpty = 13, kErrGemmAcc = 14 };
@@ -66,71 +67,93 @@ __device__ __forceinline__ uint32_t pack_act2(__half2 v) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// W^T[k, n] = fp16(fma(fp16(q), s, z)) (gemq/triton_kernels/utils.py:206-210) for k in [k0, k0+64).
-template <bool BF16, int BITS>
-__device__ __forceinline__ void dequant_row_t(unsigned char* brow, int swz, const uint32_t* wcol, size_t N, int k0,
-                                              __half s, __half z) {
-  const __half2 s2 = __half2half2(s), z2 = __half2half2(z);
-  uint32_t outw[32];  // 64 values, two per word
-  if (BITS == 3) {
-    const int w0 = k0 / 10, wl = (k0 + 63) / 10;
-    uint32_t w[8];
+// W^T[k, n] = fp16(fma(fp16(q), s, z)) (gemq/triton_kernels/utils.py:206-210) for the 32
+// reduction elements [k0, k0+32) of one output column, written as four 16-byte chunks
+// (chunk0 .. chunk0+3) of the column's swizzled 128-byte B row.
+//
+// 1/2/4-bit: `(w & mask) | 0x6400` leaves 1024 + q*2^pos in each fp16 half (codes j and
+// j + eps/2 of the word, in place); minus 1024 and times 2^-pos are exact, so the fma sees the
+// exact integer code.  A byte permute then pairs neighbouring k.
+template <bool BF16, int B>
+__device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int chunk0, const uint32_t* wcol, size_t N,
+                                               int k0, __half2 s2, __half2 z2) {
+  constexpr int EPS = 32 / B, PAIRS = EPS / 2, NPOS = 10 / B, NW = 32 / EPS;
+  constexpr uint32_t MASK = ((1u << B) - 1u) * 0x00010001u;
+  const uint32_t* wp = wcol + static_cast<size_t>(k0 / EPS) * N;
+  uint32_t w[NW];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = (w0 + i <= wl) ? wcol[static_cast<size_t>(w0 + i) * N] : 0u;
-    // position of code k0 inside word w0, then walk: at most 8 words cover 64 codes
-    int wi = 0, j = k0 - w0 * 10;
-    uint32_t cur = w[0] >> (3 * j);
+  for (int i = 0; i < NW; ++i) w[i] = wp[static_cast<size_t>(i) * N];
+  uint32_t outw[16];
+  const __half2 k1024 = __float2half2_rn(1024.f);
 #pragma unroll
-    for (int p = 0; p < 32; ++p) {
-      uint32_t q2 = 0x64006400u;
+  for (int i = 0; i < NW; ++i) {
+    __half2 v[PAIRS];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        q2 |= (cur & 7u) << (16 * h);
-        cur >>= 3;
-        if (++j == 10) {
-          j = 0;
-          ++wi;
-          // wi is data dependent only through k0 % 10: select the next word without dynamic indexing
-          uint32_t nxt = 0;
-#pragma unroll
-          for (int i = 1; i < 8; ++i) nxt = (wi == i) ? w[i] : nxt;
-          cur = nxt;
-        }
-      }
-      const __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&q2), __float2half2_rn(1024.f));
-      outw[p] = pack_act2<BF16>(__hfma2(q, s2, z2));
+    for (int q = 0; q < PAIRS; ++q) {
+      const int stage = q / NPOS, jj = q % NPOS;
+      const uint32_t bits = ((w[i] >> (stage * NPOS * B)) & (MASK << (B * jj))) | 0x64006400u;
+      __half2 c = __hsub2(*reinterpret_cast<const __half2*>(&bits), k1024);
+      if (jj > 0) c = __hmul2(c, __float2half2_rn(1.0f / static_cast<float>(1 << (B * jj))));
+      v[q] = __hfma2(c, s2, z2);
     }
-  } else {
-    constexpr int B = BITS == 3 ? 2 : BITS;
-    constexpr int EPS = 32 / B, NW = 64 / EPS;
-    constexpr uint32_t MASK = (1u << B) - 1u;
-    const uint32_t* wp = wcol + static_cast<size_t>(k0 / EPS) * N;
-    uint32_t w[NW];
 #pragma unroll
-    for (int i = 0; i < NW; ++i) w[i] = wp[static_cast<size_t>(i) * N];
-#pragma unroll
-    for (int i = 0; i < NW; ++i) {
-#pragma unroll
-      for (int j = 0; j < EPS; j += 2) {
-        // (1024 + q) as fp16 bits, minus 1024: exact integer conversion of both codes
-        const uint32_t q2 = ((w[i] >> (B * j)) & MASK) | (((w[i] >> (B * (j + 1))) & MASK) << 16) | 0x64006400u;
-        const __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&q2), __float2half2_rn(1024.f));
-        outw[(i * EPS + j) / 2] = pack_act2<BF16>(__hfma2(q, s2, z2));
-      }
+    for (int q = 0; q < PAIRS; q += 2) {
+      const uint32_t a = *reinterpret_cast<const uint32_t*>(&v[q]), bb = *reinterpret_cast<const uint32_t*>(&v[q + 1]);
+      const uint32_t lo = __byte_perm(a, bb, 0x5410), hi = __byte_perm(a, bb, 0x7632);
+      outw[(i * EPS + q) / 2] = pack_act2<BF16>(*reinterpret_cast<const __half2*>(&lo));
+      outw[(i * EPS + PAIRS + q) / 2] = pack_act2<BF16>(*reinterpret_cast<const __half2*>(&hi));
     }
   }
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
-    *reinterpret_cast<uint4*>(brow + ((c ^ swz) << 4)) = make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(brow + (((chunk0 + c) ^ swz) << 4)) =
+        make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
+}
+
+// 3-bit: 10 codes per word, the 32-element window is not word aligned: walk the codes.
+template <bool BF16>
+__device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int chunk0, const uint32_t* wcol, size_t N,
+                                             int k0, __half2 s2, __half2 z2) {
+  const int w0 = k0 / 10, wl = (k0 + 31) / 10;
+  uint32_t w[5];
+#pragma unroll
+  for (int i = 0; i < 5; ++i) w[i] = (w0 + i <= wl) ? wcol[static_cast<size_t>(w0 + i) * N] : 0u;
+  int wi = 0, j = k0 - w0 * 10;
+  uint32_t cur = w[0] >> (3 * j);
+  uint32_t outw[16];
+  const __half2 k1024 = __float2half2_rn(1024.f);
+#pragma unroll
+  for (int p = 0; p < 16; ++p) {
+    uint32_t q2 = 0x64006400u;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      q2 |= (cur & 7u) << (16 * h);
+      cur >>= 3;
+      if (++j == 10) {
+        j = 0;
+        ++wi;
+        uint32_t nxt = 0;
+#pragma unroll
+        for (int i = 1; i < 5; ++i) nxt = (wi == i) ? w[i] : nxt;
+        cur = nxt;
+      }
+    }
+    outw[p] = pack_act2<BF16>(__hfma2(__hsub2(*reinterpret_cast<const __half2*>(&q2), k1024), s2, z2));
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(brow + (((chunk0 + c) ^ swz) << 4)) =
+        make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
 }
 
 template <bool BF16>
-__device__ __forceinline__ void dequant_row(unsigned char* brow, int swz, const uint32_t* wcol, size_t N, int bits, int k0,
-                                            __half s, __half z) {
-  if (bits == 1) dequant_row_t<BF16, 1>(brow, swz, wcol, N, k0, s, z);
-  else if (bits == 2) dequant_row_t<BF16, 2>(brow, swz, wcol, N, k0, s, z);
-  else if (bits == 3) dequant_row_t<BF16, 3>(brow, swz, wcol, N, k0, s, z);
-  else dequant_row_t<BF16, 4>(brow, swz, wcol, N, k0, s, z);
+__device__ __forceinline__ void dequant32(unsigned char* brow, int swz, int chunk0, const uint32_t* wcol, size_t N,
+                                          int bits, int k0, __half s, __half z) {
+  const __half2 s2 = __half2half2(s), z2 = __half2half2(z);
+  if (bits == 1) dequant32_pow2<BF16, 1>(brow, swz, chunk0, wcol, N, k0, s2, z2);
+  else if (bits == 2) dequant32_pow2<BF16, 2>(brow, swz, chunk0, wcol, N, k0, s2, z2);
+  else if (bits == 3) dequant32_b3<BF16>(brow, swz, chunk0, wcol, N, k0, s2, z2);
+  else dequant32_pow2<BF16, 4>(brow, swz, chunk0, wcol, N, k0, s2, z2);
 }
 
 template <bool BF16>
@@ -181,14 +204,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   if (tid == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
       mbar_init(&S.a_full[s], 1);
-      mbar_init(&S.b_full[s], 4);
+      mbar_init(&S.b_full[s], kGemmProducerWarps);
       mbar_init(&S.empty[s], 1);
     }
     mbar_init(&S.acc_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) tmem_alloc(&S.tmem_base, TCOLS);
-  if (warp == 4 && lane == 0)
+  if (warp == kGemmProducerWarps + 1) tmem_alloc(&S.tmem_base, TCOLS);
+  if (warp == kGemmProducerWarps && lane == 0)
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&P.a_map)) : "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before_sync();
@@ -196,8 +219,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   tc_fence_after_sync();
   const uint32_t tmem = S.tmem_base;
 
-  if (warp < 4) {
-    // ---- B producers: thread tid owns output column n0 + tid ------------------------------
+  if (warp < kGemmProducerWarps) {
+    // ---- B producers: thread owns output column n0 + col and one 32-element half of the k-block --
+    const int col = tid & 127, kh = tid >> 7;
     const int bits = P.nbits ? P.nbits[expert] : P.fixed_bits;
     const int ngroups = P.K / P.G;
     const size_t woff = P.wq_strides ? static_cast<size_t>(P.wq_strides[expert]) : 0;
@@ -210,9 +234,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       const int k0 = kb * kGemmBK, g = k0 / P.G;
 #pragma unroll
       for (int m = 0; m < NMAT; ++m) {
-        const __half sc = P.scales[m][zoff + static_cast<size_t>(g) * N + n0 + tid];
-        const __half zr = P.zeros[m][zoff + static_cast<size_t>(g) * N + n0 + tid];
-        dequant_row<BF16>(S.b[s][m] + tid * 128, tid & 7, P.wq[m] + woff + n0 + tid, N, bits, k0, sc, zr);
+        const __half sc = P.scales[m][zoff + static_cast<size_t>(g) * N + n0 + col];
+        const __half zr = P.zeros[m][zoff + static_cast<size_t>(g) * N + n0 + col];
+        dequant32<BF16>(S.b[s][m] + col * 128, col & 7, 4 * kh, P.wq[m] + woff + n0 + col, N, bits, k0 + 32 * kh, sc, zr);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
       __syncwarp();
@@ -221,20 +245,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = tile rows -------------------------
     mbar_wait(&S.acc_full, 0, P.err, kErrGemmAcc, 64);
     tc_fence_after_sync();
-    const int r = 32 * warp + lane;
+    const int lq = warp & 3, chalf = warp >> 2;  // TMEM lane quarter of this warp, column half it drains
+    const int r = 32 * lq + lane;
     const bool row_on = r < rows;
     float rw = 1.f;
     if (!UP && P.row_weight && row_on)
       rw = BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.row_weight)[row0 + r])
                 : __half2float(static_cast<const __half*>(P.row_weight)[row0 + r]);
     unsigned char* orow = static_cast<unsigned char*>(P.out) + (static_cast<size_t>(row0 + r) * P.N + n0) * 2;
-    for (int c0 = 0; c0 < kGemmBN; c0 += 32) {
+    for (int c0 = 64 * chalf; c0 < 64 * chalf + 64; c0 += 32) {
       uint32_t d1[32];
       float v[32];
-      tmem_ld32(tmem + (static_cast<uint32_t>(32 * warp) << 16) + c0, d1);
+      tmem_ld32(tmem + (static_cast<uint32_t>(32 * lq) << 16) + c0, d1);
       if (UP) {
         uint32_t d3[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(32 * warp) << 16) + 128 + c0, d3);
+        tmem_ld32(tmem + (static_cast<uint32_t>(32 * lq) << 16) + 128 + c0, d3);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float x1 = act_round<BF16>(__uint_as_float(d1[i])), x3 = act_round<BF16>(__uint_as_float(d3[i]));
@@ -247,7 +272,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       if (row_on) store_act32<BF16>(orow + c0 * 2, v);
     }
     tc_fence_before_sync();
-  } else if (warp == 4) {
+  } else if (warp == kGemmProducerWarps) {
     // ---- A producer: one TMA box per k-block ------------------------------------------------
     if (lane == 0) {
       for (int kb = 0; kb < KB; ++kb) {
@@ -282,7 +307,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     __syncwarp();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kGemmProducerWarps + 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, TCOLS);
   }

@@ -121,9 +121,10 @@ class _QuantFusedMoEBase(nn.Module):
         sf = self._layer.shared_ffn
         return ok and (sf == 0 or (sf % 128 == 0 and self.shared_group_size % 64 == 0))
 
-    def _prefill(self, x: Tensor, route_mode: int, renorm: bool):
+    def _prefill(self, x: Tensor, route_mode: int, renorm: bool, routing=None):
         """``x [T, D]`` fp16/bf16 -> ``(out, weights, indices, logits)`` through the expert-sorted
-        tcgen05 grouped GEMM; no host synchronisation."""
+        tcgen05 grouped GEMM; no host synchronisation.  ``routing = (weights [T, A] in x.dtype,
+        indices int64 [T, A])`` skips the router."""
         dev = require_cuda(x)
         x = x.contiguous()
         T = x.shape[0]
@@ -132,7 +133,11 @@ class _QuantFusedMoEBase(nn.Module):
         if self._prefill_scratch is None or self._prefill_scratch.numel() < nbytes:
             self._prefill_scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         out = torch.empty_like(x)
-        if bf:  # the library's router reads the fp16 gate of the layer: route here with a bf16 copy
+        if routing is not None:
+            w, idx = routing[0].contiguous(), routing[1].contiguous()
+            logits = torch.empty((T, self.num_experts), dtype=torch.float32, device=dev)
+            do_route = 0
+        elif bf:  # the library's router reads the fp16 gate of the layer: route here with a bf16 copy
             w, idx, logits = self._route(x, route_mode, renorm)
             do_route = 0
         else:
