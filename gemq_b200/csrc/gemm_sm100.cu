@@ -20,11 +20,12 @@
 
 namespace gemq {
 
-constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 64;
+constexpr int kGemmBM = 256, kGemmBN = 128, kGemmBK = 64;  // CTA tile; two M=128 MMAs share every B tile
+constexpr int kMmaM = 128;
 constexpr int kGemmStages = 3;
 constexpr int kGemmProducerWarps = 8;
 constexpr int kGemmThreads = 32 * (kGemmProducerWarps + 2);  // 8 de-quantise/epilogue warps + TMA warp + MMA warp
-constexpr int kTileBytes = kGemmBM * kGemmBK * 2;  // 16 KB, A or B tile of one stage
+constexpr int kTileBytes = kGemmBN * kGemmBK * 2;  // 16 KB: a B tile, or one 128-row half of the A tile
 
 enum { kErrGemmAFull = 11, kErrGemmBFull = 12, kErrGemmEmpty = 13, kErrGemmAcc = 14 };
 
@@ -50,7 +51,7 @@ struct alignas(64) GemmParams {
 };
 
 struct GemmSmem {
-  alignas(1024) unsigned char a[kGemmStages][kTileBytes];
+  alignas(1024) unsigned char a[kGemmStages][2 * kTileBytes];
   alignas(1024) unsigned char b[kGemmStages][2][kTileBytes];
   alignas(8) unsigned long long a_full[kGemmStages], b_full[kGemmStages], empty[kGemmStages], acc_full;
   uint32_t tmem_base;
@@ -75,14 +76,10 @@ __device__ __forceinline__ uint32_t pack_act2(__half2 v) {
 // j + eps/2 of the word, in place); minus 1024 and times 2^-pos are exact, so the fma sees the
 // exact integer code.  A byte permute then pairs neighbouring k.
 template <bool BF16, int B>
-__device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int chunk0, const uint32_t* wcol, size_t N,
-                                               int k0, __half2 s2, __half2 z2) {
+__device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int chunk0, const uint32_t (&w)[5],
+                                               __half2 s2, __half2 z2) {
   constexpr int EPS = 32 / B, PAIRS = EPS / 2, NPOS = 10 / B, NW = 32 / EPS;
   constexpr uint32_t MASK = ((1u << B) - 1u) * 0x00010001u;
-  const uint32_t* wp = wcol + static_cast<size_t>(k0 / EPS) * N;
-  uint32_t w[NW];
-#pragma unroll
-  for (int i = 0; i < NW; ++i) w[i] = wp[static_cast<size_t>(i) * N];
   uint32_t outw[16];
   const __half2 k1024 = __float2half2_rn(1024.f);
 #pragma unroll
@@ -112,12 +109,9 @@ __device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int
 
 // 3-bit: 10 codes per word, the 32-element window is not word aligned: walk the codes.
 template <bool BF16>
-__device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int chunk0, const uint32_t* wcol, size_t N,
-                                             int k0, __half2 s2, __half2 z2) {
-  const int w0 = k0 / 10, wl = (k0 + 31) / 10;
-  uint32_t w[5];
-#pragma unroll
-  for (int i = 0; i < 5; ++i) w[i] = (w0 + i <= wl) ? wcol[static_cast<size_t>(w0 + i) * N] : 0u;
+__device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int chunk0, const uint32_t (&w)[5], int k0,
+                                             __half2 s2, __half2 z2) {
+  const int w0 = k0 / 10;
   int wi = 0, j = k0 - w0 * 10;
   uint32_t cur = w[0] >> (3 * j);
   uint32_t outw[16];
@@ -146,14 +140,29 @@ __device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int c
         make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
 }
 
+// Packed words of one column that cover the 32 reduction elements [k0, k0+32): at most 5.
+__device__ __forceinline__ void load_words32(uint32_t (&w)[5], const uint32_t* wcol, size_t N, int bits, int k0) {
+  int first, cnt;
+  if (bits == 3) {
+    first = k0 / 10;
+    cnt = (k0 + 31) / 10 - first + 1;
+  } else {
+    const int eps = 32 / bits;
+    first = k0 / eps;
+    cnt = 32 / eps;
+  }
+#pragma unroll
+  for (int i = 0; i < 5; ++i) w[i] = i < cnt ? wcol[static_cast<size_t>(first + i) * N] : 0u;
+}
+
 template <bool BF16>
-__device__ __forceinline__ void dequant32(unsigned char* brow, int swz, int chunk0, const uint32_t* wcol, size_t N,
-                                          int bits, int k0, __half s, __half z) {
+__device__ __forceinline__ void dequant32(unsigned char* brow, int swz, int chunk0, const uint32_t (&w)[5], int bits,
+                                          int k0, __half s, __half z) {
   const __half2 s2 = __half2half2(s), z2 = __half2half2(z);
-  if (bits == 1) dequant32_pow2<BF16, 1>(brow, swz, chunk0, wcol, N, k0, s2, z2);
-  else if (bits == 2) dequant32_pow2<BF16, 2>(brow, swz, chunk0, wcol, N, k0, s2, z2);
-  else if (bits == 3) dequant32_b3<BF16>(brow, swz, chunk0, wcol, N, k0, s2, z2);
-  else dequant32_pow2<BF16, 4>(brow, swz, chunk0, wcol, N, k0, s2, z2);
+  if (bits == 1) dequant32_pow2<BF16, 1>(brow, swz, chunk0, w, s2, z2);
+  else if (bits == 2) dequant32_pow2<BF16, 2>(brow, swz, chunk0, w, s2, z2);
+  else if (bits == 3) dequant32_b3<BF16>(brow, swz, chunk0, w, k0, s2, z2);
+  else dequant32_pow2<BF16, 4>(brow, swz, chunk0, w, s2, z2);
 }
 
 template <bool BF16>
@@ -198,7 +207,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     if (P.single_expert) expert = static_cast<int>(*P.single_expert);
   }
   constexpr int NMAT = UP ? 2 : 1;
-  constexpr uint32_t TCOLS = UP ? 256 : 128;
+  constexpr uint32_t TCOLS = UP ? 512 : 256;  // (row half, matrix) accumulators of 128 columns each
   const int KB = P.K / kGemmBK;
 
   if (tid == 0) {
@@ -228,48 +237,73 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     const size_t zoff = P.zs_strides ? static_cast<size_t>(P.zs_strides[expert])
                                      : static_cast<size_t>(expert) * ngroups * P.N;
     const size_t N = P.N;
-    for (int kb = 0; kb < KB; ++kb) {
-      const int s = kb % kGemmStages;
-      mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
-      const int k0 = kb * kGemmBK, g = k0 / P.G;
+    // Words and metadata are fetched two k-blocks ahead (register ring of three sets), so the
+    // global-load latency is off the critical path of the stage ring.
+    struct WSet { uint32_t w[NMAT][5]; __half sc[NMAT], zr[NMAT]; };
+    WSet ring[3];
+    auto fetch = [&](WSet& W, int kb) {
+      const int k0 = kb * kGemmBK + 32 * kh, g = (kb * kGemmBK) / P.G;
 #pragma unroll
       for (int m = 0; m < NMAT; ++m) {
-        const __half sc = P.scales[m][zoff + static_cast<size_t>(g) * N + n0 + col];
-        const __half zr = P.zeros[m][zoff + static_cast<size_t>(g) * N + n0 + col];
-        dequant32<BF16>(S.b[s][m] + col * 128, col & 7, 4 * kh, P.wq[m] + woff + n0 + col, N, bits, k0 + 32 * kh, sc, zr);
+        load_words32(W.w[m], P.wq[m] + woff + n0 + col, N, bits, k0);
+        W.sc[m] = P.scales[m][zoff + static_cast<size_t>(g) * N + n0 + col];
+        W.zr[m] = P.zeros[m][zoff + static_cast<size_t>(g) * N + n0 + col];
       }
+    };
+    auto produce = [&](const WSet& W, int kb) {
+      const int s = kb % kGemmStages;
+      mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m)
+        dequant32<BF16>(S.b[s][m] + col * 128, col & 7, 4 * kh, W.w[m], bits, kb * kGemmBK + 32 * kh, W.sc[m], W.zr[m]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.b_full[s]);
+    };
+    fetch(ring[0], 0);
+    if (KB > 1) fetch(ring[1], 1);
+    for (int kb0 = 0; kb0 < KB; kb0 += 3) {
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const int kb = kb0 + u;
+        if (kb < KB) {
+          if (kb + 2 < KB) fetch(ring[(u + 2) % 3], kb + 2);
+          produce(ring[u], kb);
+        }
+      }
     }
     // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = tile rows -------------------------
     mbar_wait(&S.acc_full, 0, P.err, kErrGemmAcc, 64);
     tc_fence_after_sync();
     const int lq = warp & 3, chalf = warp >> 2;  // TMEM lane quarter of this warp, column half it drains
-    const int r = 32 * lq + lane;
-    const bool row_on = r < rows;
-    float rw = 1.f;
-    if (!UP && P.row_weight && row_on)
-      rw = BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.row_weight)[row0 + r])
-                : __half2float(static_cast<const __half*>(P.row_weight)[row0 + r]);
-    unsigned char* orow = static_cast<unsigned char*>(P.out) + (static_cast<size_t>(row0 + r) * P.N + n0) * 2;
-    for (int c0 = 64 * chalf; c0 < 64 * chalf + 64; c0 += 32) {
-      uint32_t d1[32];
-      float v[32];
-      tmem_ld32(tmem + (static_cast<uint32_t>(32 * lq) << 16) + c0, d1);
-      if (UP) {
-        uint32_t d3[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(32 * lq) << 16) + 128 + c0, d3);
+    for (int hf = 0; hf < 2; ++hf) {
+      if (kMmaM * hf >= rows) break;
+      const int r = kMmaM * hf + 32 * lq + lane;
+      const bool row_on = r < rows;
+      float rw = 1.f;
+      if (!UP && P.row_weight && row_on)
+        rw = BF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(P.row_weight)[row0 + r])
+                  : __half2float(static_cast<const __half*>(P.row_weight)[row0 + r]);
+      unsigned char* orow = static_cast<unsigned char*>(P.out) + (static_cast<size_t>(row0 + r) * P.N + n0) * 2;
+      const uint32_t tbase = tmem + (static_cast<uint32_t>(32 * lq) << 16) + hf * NMAT * 128;
+      for (int c0 = 64 * chalf; c0 < 64 * chalf + 64; c0 += 32) {
+        uint32_t d1[32];
+        float v[32];
+        tmem_ld32(tbase + c0, d1);
+        if (UP) {
+          uint32_t d3[32];
+          tmem_ld32(tbase + 128 + c0, d3);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x1 = act_round<BF16>(__uint_as_float(d1[i])), x3 = act_round<BF16>(__uint_as_float(d3[i]));
-          v[i] = act_round<BF16>(silu_f32(x1)) * x3;  // F.silu(x1) * x3 on activation-dtype tensors
+          for (int i = 0; i < 32; ++i) {
+            const float x1 = act_round<BF16>(__uint_as_float(d1[i])), x3 = act_round<BF16>(__uint_as_float(d3[i]));
+            v[i] = act_round<BF16>(silu_f32(x1)) * x3;  // F.silu(x1) * x3 on activation-dtype tensors
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = act_round<BF16>(__uint_as_float(d1[i])) * rw;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = act_round<BF16>(__uint_as_float(d1[i])) * rw;
+        if (row_on) store_act32<BF16>(orow + c0 * 2, v);
       }
-      if (row_on) store_act32<BF16>(orow + c0 * 2, v);
     }
     tc_fence_before_sync();
   } else if (warp == kGemmProducerWarps) {
@@ -278,14 +312,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       for (int kb = 0; kb < KB; ++kb) {
         const int s = kb % kGemmStages;
         mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
-        mbar_arrive_expect_tx(&S.a_full[s], kTileBytes);
+        mbar_arrive_expect_tx(&S.a_full[s], 2 * kTileBytes);
         tma_load_2d(S.a[s], &P.a_map, kb * kGemmBK, row0, &S.a_full[s]);
       }
     }
   } else {
     // ---- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(BF16 ? 1 : 0, kGemmBM, kGemmBN);
+      const uint32_t idesc = umma_idesc_f16(BF16 ? 1 : 0, kMmaM, kGemmBN);
+      const int halves = rows > kMmaM ? 2 : 1;
       for (int kb = 0; kb < KB; ++kb) {
         const int s = kb % kGemmStages;
         const uint32_t par = (kb / kGemmStages) & 1;
@@ -295,10 +330,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         const uint32_t a_addr = smem_u32(S.a[s]);
 #pragma unroll
         for (int k4 = 0; k4 < kGemmBK / 16; ++k4) {
-          const uint64_t ad = umma_desc_k_sw128(a_addr + k4 * 32);
 #pragma unroll
-          for (int m = 0; m < NMAT; ++m)
-            umma_f16(tmem + 128 * m, ad, umma_desc_k_sw128(smem_u32(S.b[s][m]) + k4 * 32), idesc, (kb | k4) != 0);
+          for (int m = 0; m < NMAT; ++m) {
+            const uint64_t bd = umma_desc_k_sw128(smem_u32(S.b[s][m]) + k4 * 32);
+            for (int hf = 0; hf < halves; ++hf)
+              umma_f16(tmem + (hf * NMAT + m) * 128, umma_desc_k_sw128(a_addr + hf * kTileBytes + k4 * 32), bd, idesc,
+                       (kb | k4) != 0);
+          }
         }
         umma_commit(&S.empty[s]);  // stage is free once these MMAs have read it
       }
@@ -360,27 +398,6 @@ __global__ void prefill_plan_kernel(PrefillPlan pl, int E, int max_tiles) {
   *pl.n_tiles = nt;
 }
 
-// One warp per (token, slot): claim a row in the expert's segment, copy the activation row there.
-template <typename T>
-__global__ void prefill_scatter_kernel(PrefillPlan pl, const long long* __restrict__ idx, const T* __restrict__ w,
-                                       const T* __restrict__ x, T* __restrict__ xs, T* __restrict__ row_w, int n,
-                                       int A, int D) {
-  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (i >= n) return;
-  int pos = 0;
-  if (lane == 0) {
-    const int e = static_cast<int>(idx[i]);
-    pos = pl.offsets[e] + atomicAdd(&pl.cursor[e], 1);
-    pl.inv[i] = pos;
-    row_w[pos] = w[i];
-  }
-  pos = __shfl_sync(0xffffffffu, pos, 0);
-  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(i / A) * D);
-  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(pos) * D);
-  for (int k = lane; k < D / 8; k += 32) dst[k] = src[k];
-}
-
 template <typename T> struct ActT;
 template <> struct ActT<__half> {
   static __device__ __forceinline__ float f(__half v) { return __half2float(v); }
@@ -391,13 +408,52 @@ template <> struct ActT<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat16 r(float v) { return __float2bfloat16_rn(v); }
 };
 
+template <typename T>
+__device__ __forceinline__ uint4 to_half8(uint4 v) {
+  const T* p = reinterpret_cast<const T*>(&v);
+  uint4 o;
+  __half2* q = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) q[i] = __floats2half2_rn(ActT<T>::f(p[2 * i]), ActT<T>::f(p[2 * i + 1]));
+  return o;
+}
+
+// One warp per (token, slot): claim a row in the expert's segment, copy the activation row there.
+// bf16 activations are converted to fp16 here: the GEMMs then run entirely in fp16 like the
+// reference model does, and the fp16 de-quantised weights need no second rounding.
+template <typename T>
+__global__ void prefill_scatter_kernel(PrefillPlan pl, const long long* __restrict__ idx, const T* __restrict__ w,
+                                       const T* __restrict__ x, __half* __restrict__ xs, __half* __restrict__ row_w,
+                                       int n, int A, int D) {
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (i >= n) return;
+  int pos = 0;
+  if (lane == 0) {
+    const int e = static_cast<int>(idx[i]);
+    pos = pl.offsets[e] + atomicAdd(&pl.cursor[e], 1);
+    pl.inv[i] = pos;
+    row_w[pos] = __float2half_rn(ActT<T>::f(w[i]));
+  }
+  pos = __shfl_sync(0xffffffffu, pos, 0);
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(i / A) * D);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(pos) * D);
+  for (int k = lane; k < D / 8; k += 32) dst[k] = to_half8<T>(src[k]);
+}
+
+template <typename T>
+__global__ void to_half_kernel(const T* __restrict__ x, __half* __restrict__ y, size_t n8) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n8) reinterpret_cast<uint4*>(y)[i] = to_half8<T>(reinterpret_cast<const uint4*>(x)[i]);
+}
+
 // out[t] = contributions of the token's experts added in increasing expert id, each addition
 // rounded to the activation dtype (index_add_ in the loop of moe_block.py:191-195), then the
 // shared-expert output (moe_block.py:483).
 template <typename T>
 __global__ void prefill_combine_kernel(const int* __restrict__ inv, const long long* __restrict__ idx,
-                                       const T* __restrict__ ys, const T* __restrict__ shared, T* __restrict__ out,
-                                       int tokens, int A, int D) {
+                                       const __half* __restrict__ ys, const __half* __restrict__ shared,
+                                       T* __restrict__ out, int tokens, int A, int D) {
   const int t = blockIdx.x;
   int order[kMaxSlots];
   for (int a = 0; a < A; ++a) order[a] = a;
@@ -409,9 +465,10 @@ __global__ void prefill_combine_kernel(const int* __restrict__ inv, const long l
     float acc = 0.f;
     for (int a = 0; a < A; ++a) {
       const int row = inv[t * A + order[a]];
-      acc = ActT<T>::f(ActT<T>::r(acc + ActT<T>::f(ys[static_cast<size_t>(row) * D + d])));
+      const float c = ActT<T>::f(ActT<T>::r(__half2float(ys[static_cast<size_t>(row) * D + d])));
+      acc = ActT<T>::f(ActT<T>::r(acc + c));
     }
-    if (shared) acc = ActT<T>::f(ActT<T>::r(acc + ActT<T>::f(shared[static_cast<size_t>(t) * D + d])));
+    if (shared) acc = ActT<T>::f(ActT<T>::r(acc + ActT<T>::f(ActT<T>::r(__half2float(shared[static_cast<size_t>(t) * D + d])))));
     out[static_cast<size_t>(t) * D + d] = ActT<T>::r(acc);
   }
 }
@@ -459,6 +516,7 @@ struct PrefillScratch {
   void* ys;     // [R, D]
   void* hs;     // [T, SF]
   void* yss;    // [T, D]
+  void* xh;     // [T, D] fp16 copy of bf16 activations (shared experts)
   int max_tiles;
 };
 
@@ -482,6 +540,7 @@ size_t prefill_bytes(const gemq_moe_layer_t* L, int tokens, PrefillScratch* S, c
   char* ys = take(2 * R * L->hidden);
   char* hs = take(L->shared_ffn ? 2 * static_cast<size_t>(tokens) * L->shared_ffn : 0);
   char* yss = take(L->shared_ffn ? 2 * static_cast<size_t>(tokens) * L->hidden : 0);
+  char* xh = take(L->shared_ffn ? 2 * static_cast<size_t>(tokens) * L->hidden : 0);
   if (S) {
     S->plan.counts = reinterpret_cast<int*>(counts);
     S->plan.cursor = reinterpret_cast<int*>(cursor);
@@ -492,7 +551,7 @@ size_t prefill_bytes(const gemq_moe_layer_t* L, int tokens, PrefillScratch* S, c
     S->plan.tile_row0 = reinterpret_cast<int*>(tr0);
     S->plan.tile_rows = reinterpret_cast<int*>(trn);
     S->plan.inv = reinterpret_cast<int*>(inv);
-    S->row_w = roww; S->xs = xs; S->h = h; S->ys = ys; S->hs = hs; S->yss = yss;
+    S->row_w = roww; S->xs = xs; S->h = h; S->ys = ys; S->hs = hs; S->yss = yss; S->xh = xh;
     S->max_tiles = max_tiles;
   }
   return off;
@@ -567,7 +626,7 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
   if (bf)
     prefill_scatter_kernel<__nv_bfloat16><<<cdiv(R, 8), 256, 0, st>>>(
         S.plan, reinterpret_cast<const long long*>(idx), static_cast<const __nv_bfloat16*>(w),
-        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(S.xs), static_cast<__nv_bfloat16*>(S.row_w), R, A, D);
+        static_cast<const __nv_bfloat16*>(x), static_cast<__half*>(S.xs), static_cast<__half*>(S.row_w), R, A, D);
   else
     prefill_scatter_kernel<__half><<<cdiv(R, 8), 256, 0, st>>>(
         S.plan, reinterpret_cast<const long long*>(idx), static_cast<const __half*>(w), static_cast<const __half*>(x),
@@ -585,7 +644,7 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
   U.N = F; U.K = D; U.G = G;
   U.out = S.h;
   U.err = S.err;
-  if (int rc = launch_gemm(U, true, bf, S.max_tiles, st)) return rc;
+  if (int rc = launch_gemm(U, true, false, S.max_tiles, st)) return rc;
 
   // down GEMM, scaled by the routing weight
   GemmParams Dn = {};
@@ -598,11 +657,18 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
   Dn.out = S.ys;
   Dn.row_weight = S.row_w;
   Dn.err = S.err;
-  if (int rc = launch_gemm(Dn, false, bf, S.max_tiles, st)) return rc;
+  if (int rc = launch_gemm(Dn, false, false, S.max_tiles, st)) return rc;
 
   if (SF) {  // shared experts on all tokens (moe_block.py:419-430)
+    const void* xsh = x;
+    if (bf) {
+      const size_t n8 = static_cast<size_t>(tokens) * D / 8;
+      to_half_kernel<__nv_bfloat16><<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<__half*>(S.xh), n8);
+      xsh = S.xh;
+    }
     GemmParams SU = {};
-    if (!tensor_map_2d(&SU.a_map, x, 2, D, tokens, kGemmBK, kGemmBM, true)) return GEMQ_ERR_LAUNCH;
+    if (!tensor_map_2d(&SU.a_map, xsh, 2, D, tokens, kGemmBK, kGemmBM, true)) return GEMQ_ERR_LAUNCH;
     fill_single(SU, 0, L->s1);
     fill_single(SU, 1, L->s3);
     SU.fixed_bits = L->s1.nbits;
@@ -610,7 +676,7 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
     SU.N = SF; SU.K = D; SU.G = L->s1.group_size;
     SU.out = S.hs;
     SU.err = S.err;
-    if (int rc = launch_gemm(SU, true, bf, cdiv(tokens, kGemmBM), st)) return rc;
+    if (int rc = launch_gemm(SU, true, false, cdiv(tokens, kGemmBM), st)) return rc;
     GemmParams SD = {};
     if (!tensor_map_2d(&SD.a_map, S.hs, 2, SF, tokens, kGemmBK, kGemmBM, true)) return GEMQ_ERR_LAUNCH;
     fill_single(SD, 0, L->s2);
@@ -619,12 +685,12 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
     SD.N = D; SD.K = SF; SD.G = L->s2.group_size;
     SD.out = S.yss;
     SD.err = S.err;
-    if (int rc = launch_gemm(SD, false, bf, cdiv(tokens, kGemmBM), st)) return rc;
+    if (int rc = launch_gemm(SD, false, false, cdiv(tokens, kGemmBM), st)) return rc;
   }
   if (bf)
     prefill_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, st>>>(
-        S.plan.inv, reinterpret_cast<const long long*>(idx), static_cast<const __nv_bfloat16*>(S.ys),
-        SF ? static_cast<const __nv_bfloat16*>(S.yss) : nullptr, static_cast<__nv_bfloat16*>(out), tokens, A, D);
+        S.plan.inv, reinterpret_cast<const long long*>(idx), static_cast<const __half*>(S.ys),
+        SF ? static_cast<const __half*>(S.yss) : nullptr, static_cast<__nv_bfloat16*>(out), tokens, A, D);
   else
     prefill_combine_kernel<__half><<<tokens, 256, 0, st>>>(
         S.plan.inv, reinterpret_cast<const long long*>(idx), static_cast<const __half*>(S.ys),
