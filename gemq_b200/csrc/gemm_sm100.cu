@@ -23,7 +23,7 @@ namespace gemq {
 constexpr int kGemmBM = 256, kGemmBN = 128, kGemmBK = 64;  // CTA tile; two M=128 MMAs share every B tile
 constexpr int kMmaM = 128;
 constexpr int kGemmStages = 3;
-constexpr int kGemmProducerWarps = 8;
+constexpr int kGemmProducerWarps = 16;
 constexpr int kGemmThreads = 32 * (kGemmProducerWarps + 2);  // 8 de-quantise/epilogue warps + TMA warp + MMA warp
 constexpr int kTileBytes = kGemmBN * kGemmBK * 2;  // 16 KB: a B tile, or one 128-row half of the A tile
 
@@ -89,8 +89,10 @@ __device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int
     for (int q = 0; q < PAIRS; ++q) {
       const int stage = q / NPOS, jj = q % NPOS;
       const uint32_t bits = ((w[i] >> (stage * NPOS * B)) & (MASK << (B * jj))) | 0x64006400u;
-      __half2 c = __hsub2(*reinterpret_cast<const __half2*>(&bits), k1024);
-      if (jj > 0) c = __hmul2(c, __float2half2_rn(1.0f / static_cast<float>(1 << (B * jj))));
+      // (1024 + q*2^pos) * 2^-pos - 1024 * 2^-pos = q, exactly, in one fma
+      constexpr float kInv[10] = {1.f, 1.f / 2, 1.f / 4, 1.f / 8, 1.f / 16, 1.f / 32, 1.f / 64, 1.f / 128, 1.f / 256, 1.f / 512};
+      const float inv = kInv[B * jj];
+      const __half2 c = __hfma2(*reinterpret_cast<const __half2*>(&bits), __float2half2_rn(inv), __float2half2_rn(-1024.f * inv));
       v[q] = __hfma2(c, s2, z2);
     }
 #pragma unroll
@@ -213,7 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   if (tid == 0) {
     for (int s = 0; s < kGemmStages; ++s) {
       mbar_init(&S.a_full[s], 1);
-      mbar_init(&S.b_full[s], kGemmProducerWarps);
+      mbar_init(&S.b_full[s], kGemmProducerWarps / 2);  // the warp group that owns the k-block
       mbar_init(&S.empty[s], 1);
     }
     mbar_init(&S.acc_full, 1);
@@ -230,7 +232,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 
   if (warp < kGemmProducerWarps) {
     // ---- B producers: thread owns output column n0 + col and one 32-element half of the k-block --
-    const int col = tid & 127, kh = tid >> 7;
+    // Two groups of 8 warps take alternate k-blocks, so twice as many warps hide the latencies of
+    // the de-quantisation chain.  Inside a group: one thread per column and 32-element half.
+    const int grp = tid >> 8, col = tid & 127, kh = (tid >> 7) & 1;
     const int bits = P.nbits ? P.nbits[expert] : P.fixed_bits;
     const int ngroups = P.K / P.G;
     const size_t woff = P.wq_strides ? static_cast<size_t>(P.wq_strides[expert]) : 0;
@@ -260,14 +264,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.b_full[s]);
     };
-    fetch(ring[0], 0);
-    if (KB > 1) fetch(ring[1], 1);
-    for (int kb0 = 0; kb0 < KB; kb0 += 3) {
+    if (grp < KB) fetch(ring[0], grp);
+    if (grp + 2 < KB) fetch(ring[1], grp + 2);
+    for (int kb0 = grp; kb0 < KB; kb0 += 6) {
 #pragma unroll
       for (int u = 0; u < 3; ++u) {
-        const int kb = kb0 + u;
+        const int kb = kb0 + 2 * u;
         if (kb < KB) {
-          if (kb + 2 < KB) fetch(ring[(u + 2) % 3], kb + 2);
+          if (kb + 4 < KB) fetch(ring[(u + 2) % 3], kb + 4);
           produce(ring[u], kb);
         }
       }
@@ -275,7 +279,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = tile rows -------------------------
     mbar_wait(&S.acc_full, 0, P.err, kErrGemmAcc, 64);
     tc_fence_after_sync();
-    const int lq = warp & 3, chalf = warp >> 2;  // TMEM lane quarter of this warp, column half it drains
+    const int lq = warp & 3, cq = warp >> 2;  // TMEM lane quarter of this warp, 32-column quarter it drains
     for (int hf = 0; hf < 2; ++hf) {
       if (kMmaM * hf >= rows) break;
       const int r = kMmaM * hf + 32 * lq + lane;
@@ -286,7 +290,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                   : __half2float(static_cast<const __half*>(P.row_weight)[row0 + r]);
       unsigned char* orow = static_cast<unsigned char*>(P.out) + (static_cast<size_t>(row0 + r) * P.N + n0) * 2;
       const uint32_t tbase = tmem + (static_cast<uint32_t>(32 * lq) << 16) + hf * NMAT * 128;
-      for (int c0 = 64 * chalf; c0 < 64 * chalf + 64; c0 += 32) {
+      for (int c0 = 32 * cq; c0 < 32 * cq + 32; c0 += 32) {
         uint32_t d1[32];
         float v[32];
         tmem_ld32(tbase + c0, d1);
