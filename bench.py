@@ -36,6 +36,9 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=8)
     p.add_argument("--cpu-sample-cols", type=int, default=1792)
+    p.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                   help="decode: config 1 (default, the headline metric); prefill: config 3, 4096-token grouped GEMM, "
+                        "expert-parallel over the ranks when launched with torchrun")
     p.add_argument("--mode", default="bench", choices=["bench", "up_only", "layer_only"],
                    help="up_only / layer_only: a short eager loop of one op for profilers; prints its own timing")
     return p.parse_args()
@@ -180,6 +183,84 @@ def profile_loop(args, blocks, xs, pairs, dev):
                       "bits_of_selected_experts": bits[:args.steps + args.warmup]}))
 
 
+def run_prefill(args, rank, local_rank, world):
+    """Config 3: Mixtral-shaped layer, 4096 bf16 tokens, top-2 with Dirichlet(0.5) expert popularity,
+    mixed bits.  One GPU: expert-sorted grouped GEMM.  N GPUs: experts sharded, tokens exchanged with
+    all-to-all (strong scaling: the 4096 tokens are split over the ranks)."""
+    import torch
+    import torch.distributed as dist
+    from gemq_b200 import synth
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    T, top_k = 4096, A
+    g = torch.Generator().manual_seed(7)
+    pop = torch.distributions.Dirichlet(torch.full((E,), 0.5)).sample() if False else None
+    torch.manual_seed(7)
+    pop = torch.distributions.Dirichlet(torch.full((E,), 0.5)).sample()
+    sel_all = torch.multinomial(pop.expand(T, E), top_k, replacement=False, generator=g)
+    w_all = torch.softmax(torch.randn(T, top_k, generator=g), -1).to(torch.bfloat16)
+    x_all = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    lo, hi = rank * T // world, (rank + 1) * T // world
+    xh = x_all[lo:hi].contiguous().pin_memory()
+    x, w, sel = xh.to(dev), w_all[lo:hi].to(dev), sel_all[lo:hi].to(dev)
+    if world > 1:
+        layer, bits = synth.mixtral_expert_parallel(rank, world, seed=0, device=dev)
+        step = lambda xin: layer.forward_routed(xin, w, sel)
+    else:
+        blk = synth.mixtral_block(seed=0, device=dev)
+        bits = blk._nbits_host
+        step = lambda xin: blk._prefill(xin, 1, True, routing=(w, sel))[0]
+    for _ in range(args.warmup):
+        step(x)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step(x)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    oh = torch.empty(hi - lo, D, dtype=torch.bfloat16).pin_memory()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        out = step(xh.to(dev, non_blocking=True))
+        oh.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms, e2e_s * 1e3], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1]) * 1e-3
+    if rank == 0:
+        flops = 2.0 * T * top_k * 3 * D * FFN
+        peak_tf = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"] if os.path.exists(
+            os.path.join(ROOT, "MEASURED_PEAKS.json")) else 1590.0
+        ach = flops / (ms / args.steps * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "moe_layer_prefill_tokens_per_s", "value": T * args.steps / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "mixtral8x7b_moe_layer_prefill_4096tok_top2_dirichlet0.5_mixed_bits (config 3)",
+                       "bits": bits, "tokens_per_rank": hi - lo, "parallelism": f"expert-parallel x{world}",
+                       "l2": "inputs larger than L2: ~0.4 GB of packed weights per step"},
+            "e2e": {"value": T * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * D // world,
+                    "d2h_bytes_per_step": 2 * T * D // world},
+            "gpu_launches": 7 * args.steps, "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (gate/up + down; whole prefill call timed)",
+                         "achieved": ach / world, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / world / peak_tf,
+                         "traffic": None}}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -187,6 +268,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "prefill":
+        run_prefill(args, rank, local_rank, world)
         return
 
     import torch

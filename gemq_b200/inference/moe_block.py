@@ -30,6 +30,21 @@ def _excl_cumsum(vals, device):
     return t.to(torch.int32).to(device)
 
 
+def route_tokens(x: Tensor, gate_weight: Tensor, top_k: int, mode: int, renorm: bool):
+    """Router on the device: ``(weights [T, A] in x.dtype, indices int64 [T, A], logits fp32 [T, E])``."""
+    dev = require_cuda(x, gate_weight)
+    T, D = x.shape
+    E = gate_weight.shape[0]
+    idx = torch.empty((T, top_k), dtype=torch.int64, device=dev)
+    w = torch.empty((T, top_k), dtype=x.dtype, device=dev)
+    logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+    gate = gate_weight if gate_weight.dtype == x.dtype else gate_weight.to(x.dtype)
+    _capi.check("gemq_moe_route", _capi.lib.gemq_moe_route(
+        x.data_ptr(), gate.contiguous().data_ptr(), T, D, E, top_k, mode, int(renorm),
+        int(x.dtype == torch.bfloat16), idx.data_ptr(), w.data_ptr(), logits.data_ptr(), stream_ptr(dev)))
+    return w, idx, logits
+
+
 class _QuantFusedMoEBase(nn.Module):
     """State and dispatch shared by the two model families."""
 

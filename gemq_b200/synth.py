@@ -73,3 +73,25 @@ def deepseek_block(seed: int = 0, device="cuda", bits=None, shared_bits: int = 4
     shared = (make_linear(SF, D, shared_bits, group, gen, device), make_linear(D, SF, shared_bits, group, gen, device),
               make_linear(SF, D, shared_bits, group, gen, device))
     return QuantFusedDeepseekV2MoEBlock.from_linears(cfg, gate, w1, w2, w3, shared)
+
+
+def mixtral_expert_parallel(rank: int, world: int, seed: int = 0, device="cuda", bits=None, group: int = 128,
+                            process_group=None, **overrides):
+    """This rank's shard of a Mixtral-shaped layer: experts ``[rank*E/world, (rank+1)*E/world)``.
+    Every expert is drawn from its own seed, so all ranks agree on the full layer."""
+    from .inference.expert_parallel import ExpertParallelMixtralMoE
+    cfg = {**MIXTRAL_8X7B, **overrides}
+    E, D, Fd, A = cfg["num_local_experts"], cfg["hidden_size"], cfg["intermediate_size"], cfg["num_experts_per_tok"]
+    assert E % world == 0
+    bits = bits or draw_expert_bits(E, seed)
+    gate = (torch.randn(E, D, device=device, generator=generator(seed, device)) * 0.02).to(torch.float16)
+    lo, hi = rank * E // world, (rank + 1) * E // world
+    w1, w2, w3 = [], [], []
+    for e in range(lo, hi):
+        gen = generator(seed * 1000 + 17 * e + 1, device)
+        w1.append(make_linear(Fd, D, bits[e], group, gen, device))
+        w3.append(make_linear(Fd, D, bits[e], group, gen, device))
+        w2.append(make_linear(D, Fd, bits[e], group, gen, device))
+    local_cfg = SimpleNamespace(hidden_size=D, intermediate_size=Fd, num_local_experts=hi - lo, num_experts_per_tok=1)
+    local = QuantFusedMixtralMoEBlock.from_linears(local_cfg, gate[lo:hi].clone(), w1, w2, w3)
+    return ExpertParallelMixtralMoE(local, gate, E, A, process_group), bits

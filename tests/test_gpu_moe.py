@@ -171,3 +171,43 @@ def test_deepseek_prefill_with_shared_experts_bf16():
     got = out.float().cpu().numpy()
     # bf16 activations and bf16-rounded weights: 8 mantissa bits
     assert rel_fro(got, ref) < 2e-2
+
+
+def _ep_worker(rank, world, port, results):
+    import os
+    import torch.distributed as dist
+    from gemq_b200 import synth
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dims = dict(hidden_size=256, intermediate_size=512, num_local_experts=4, num_experts_per_tok=2)
+    bits = [1, 2, 3, 4]
+    ep, _ = synth.mixtral_expert_parallel(rank, world, seed=5, device=dev, bits=bits, **dims)
+    full, _ = synth.mixtral_expert_parallel(0, 1, seed=5, device=dev, bits=bits, **dims)  # all experts, no exchange
+    g = torch.Generator().manual_seed(11 + rank)
+    T = 150 + 20 * rank
+    x = torch.randn(T, 256, generator=g).half().to(dev)
+    sel = torch.stack([torch.randperm(4, generator=g)[:2] for _ in range(T)]).to(dev)
+    w = torch.softmax(torch.randn(T, 2, generator=g), -1).half().to(dev)
+    y = ep.forward_routed(x, w, sel)
+    # single-GPU result with the same routing: every row through its expert, same combine
+    from gemq_b200.inference.expert_parallel import combine_in_expert_order
+    rows = x.repeat_interleave(2, 0)
+    yy = full.local._prefill(rows, 1, True, routing=(w.reshape(-1, 1), sel.reshape(-1, 1)))[0]
+    ref = combine_in_expert_order(yy.view(T, 2, -1), sel)
+    results[rank] = float((y.float() - ref.float()).abs().max())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_two_gpus_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_ep_worker, args=(2, 29611, results), nprocs=2, join=True)
+    assert max(results.values()) == 0.0, dict(results)
