@@ -204,6 +204,29 @@ int gemq_moe_prefill(const gemq_moe_layer_t* layer, const void* x, void* out, in
 /* Device address of the error word gemq_moe_prefill writes in `scratch` (0 = every wait was met). */
 const int32_t* gemq_moe_prefill_error_word(const gemq_moe_layer_t* layer, int tokens, void* scratch);
 
+/* ---- for callers that cannot allocate --------------------------------------------------------- */
+
+/* No counterpart in the reference.  y[1, N] = x[1, K] @ deq(wq), the same result as
+ * gemq_dequant_gemv with tokens == 1, but without a caller-provided workspace: the split-K
+ * scratch lives in a fixed 2 MiB device array inside the library (gemq_static_scratch_bytes),
+ * held by every GPU that loads the library until the process exits.  Nothing is allocated
+ * or freed, here or in anything it calls.  For hosts that must not allocate on this path: a
+ * serving process with a frozen memory pool, a plugin inside a runtime that forbids
+ * cudaMalloc after start-up, code running during stream capture.
+ *   - Returns GEMQ_ERR_WORKSPACE when gemq_gemv_workspace_bytes(N, K, 1) exceeds the array
+ *     (roughly N * ceil(K / 512) > 490,000), GEMQ_ERR_BAD_ARG on null pointers or bad extents.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the one array, and the array keeps what the last call left
+ *     in it; every call first clears the part it reads.  Two calls that overlap on the GPU
+ *     (different streams, no ordering between them) race on it: order them. */
+int gemq_dequant_gemv_static(const void* x, const int32_t* wq, const void* scales, const void* zeros,
+                             void* y, int N, int K, int nbits, int group_size, gemq_stream_t stream);
+
+/* Capacity in bytes of the built-in scratch used by gemq_dequant_gemv_static. */
+size_t gemq_static_scratch_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif
