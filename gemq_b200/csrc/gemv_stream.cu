@@ -60,9 +60,11 @@ struct StageBuf {
   alignas(1024) unsigned char words[4 * kStripBytes];
   alignas(16) __half scales[kMaxUnitGroups][128];
   alignas(16) __half zeros[kMaxUnitGroups][128];
-  alignas(16) uint32_t tab[1024];   // 1/2/4-bit: [64 rows][eps halves]; 3-bit: [2 variants][64 rows][16 halves]
+  // 1/2/4-bit: [3 digit planes][64 rows][8/B words of s8 digits], planes padded apart (kPlaneStride);
+  // 3-bit: [2 variants][64 rows][16 halves]
+  alignas(16) uint32_t tab[2048 + 64];
   float xsum[kMaxUnitGroups];       // sum of the activations of each group
-  float fin[kMaxUnitGroups];        // 2^(24 - c_g): undoes the subnormal and activation scaling of each group
+  float fin[kMaxUnitGroups];        // power of two that undoes the operand scaling of each group
 };
 
 struct JobInfo {
@@ -232,11 +234,40 @@ __device__ __forceinline__ int scale_exponent(float mx) {
   return c < -15 ? -15 : (c > 40 ? 40 : c);
 }
 
-// 1/2/4-bit: lane handles word rows `lane` and `lane + 32`.  A group is 4*B consecutive rows,
-// so its maximum and sum are reductions over 4*B neighbouring lanes.
+// ---- 1/2/4-bit units: integer operands ------------------------------------------------------
+// A word ANDed with a per-byte mask is a ready u8 A operand of mma.sync.m16n8k32 (u8 x s8 ->
+// s32) with four codes in it, each shifted left by its position inside the byte: code j of a
+// word (bit B*j) sits in byte j / (8/B) at in-byte position B * (j % (8/B)); operand q of a
+// word collects the codes {y * 8/B + q : y = 0..3}, all at position pos = B*q.  One AND per
+// four codes, no shifts.
+// The activations of a group are scaled by 2^(c - pos) so that the largest lies in
+// [2^22, 2^23), rounded to an integer and split into three balanced base-256 digits
+// (each in [-128, 127]).  Digit plane pl of the table is an s8 B operand worth 256^pl; the
+// planes of two consecutive groups occupy MMA columns 0..2 and 4..6.  The integer
+// accumulation is exact.  (mma.sync with e4m3 operands would need half as many planes, but
+// on sm_100a it costs 23 to 44 issue cycles once its operands change between instructions,
+// against 8 for the integer form; the 4-bit integer forms are slower still.)
+template <int B>
+struct I8Fmt {
+  static constexpr int kCpb = 8 / B;      // codes per byte = operands per word
+  static constexpr int kWin = 2 * B;      // loop iterations per pair of groups
+  static constexpr int kPlaneStride = 64 * kCpb + (B == 1 ? 4 : (B == 2 ? 16 : 8));  // words; the pad spreads the planes over the banks
+  static constexpr uint32_t kMask = ((1u << B) - 1u) * 0x01010101u;
+  __device__ static __forceinline__ uint32_t operand(uint32_t w, int q) { return w & (kMask << (B * q)); }
+};
+
+// c = 22 - floor(log2(max|x|)) of a group: the largest scaled value lands in [2^22, 2^23).
+__device__ __forceinline__ int scale_exponent_i8(float mx) {
+  int c = 22 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
+  return c < -15 ? -15 : (c > 60 ? 60 : c);
+}
+
+// Lane handles word rows `lane` and `lane + 32`.  A group is 4*B consecutive rows, so its
+// maximum and sum are reductions over 4*B neighbouring lanes.
 template <int B, bool XF32>
-__device__ __forceinline__ void build_table_pow2(StageBuf& T, const void* x, const Unit& U) {
-  constexpr int EPS = 32 / B, PAIRS = EPS / 2, NPOS = 10 / B, LPG = 4 * B;
+__device__ __forceinline__ void build_table_i8(StageBuf& T, const void* x, const Unit& U) {
+  using F = I8Fmt<B>;
+  constexpr int EPS = 32 / B, CPB = F::kCpb, LPG = 4 * B;
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
@@ -277,24 +308,40 @@ __device__ __forceinline__ void build_table_pow2(StageBuf& T, const void* x, con
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       sm += __shfl_xor_sync(0xffffffffu, sm, o);
     }
-    const int c = scale_exponent(mx);
+    const int c = scale_exponent_i8(mx);
     if (on && (lane % LPG) == 0) {
       T.xsum[row / LPG] = sm;
-      T.fin[row / LPG] = pow2i(24 - c);
+      T.fin[row / LPG] = pow2i(-c);
     }
     if (on) {
-      uint32_t outw[PAIRS];
-#pragma unroll
+      constexpr int QB = CPB >= 4 ? 4 : CPB;  // operands per store
       const float fb = pow2i(c);
 #pragma unroll
-      for (int q = 0; q < PAIRS; ++q) {
-        const float f = fb * (1.0f / static_cast<float>(1 << (B * (q % NPOS))));
-        const __half2 h = __floats2half2_rn(xv[q] * f, xv[q + PAIRS] * f);
-        outw[q] = *reinterpret_cast<const uint32_t*>(&h);
-      }
-      uint4* dst = reinterpret_cast<uint4*>(T.tab + row * PAIRS);
+      for (int q0 = 0; q0 < CPB; q0 += QB) {
+        uint32_t pl[3][QB];
 #pragma unroll
-      for (int i = 0; i < PAIRS / 4; ++i) dst[i] = make_uint4(outw[4 * i], outw[4 * i + 1], outw[4 * i + 2], outw[4 * i + 3]);
+        for (int qq = 0; qq < QB; ++qq) {
+          const int q = q0 + qq;
+          const float f = fb * (1.0f / static_cast<float>(1 << (B * q)));
+          int d0[4], d1[4], d2[4];
+#pragma unroll
+          for (int y = 0; y < 4; ++y) {
+            d0[y] = __float2int_rn(xv[y * CPB + q] * f);
+            d1[y] = (d0[y] + 128) >> 8;
+            d2[y] = (d1[y] + 128) >> 8;
+          }
+          // the low bytes of the four values of each digit, one per operand byte
+          pl[0][qq] = __byte_perm(__byte_perm(d0[0], d0[1], 0x0040), __byte_perm(d0[2], d0[3], 0x0040), 0x5410);
+          pl[1][qq] = __byte_perm(__byte_perm(d1[0], d1[1], 0x0040), __byte_perm(d1[2], d1[3], 0x0040), 0x5410);
+          pl[2][qq] = __byte_perm(__byte_perm(d2[0], d2[1], 0x0040), __byte_perm(d2[2], d2[3], 0x0040), 0x5410);
+        }
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+          uint32_t* dst = T.tab + p * F::kPlaneStride + row * CPB + q0;
+          if (QB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(pl[p][0], pl[p][1], pl[p][2], pl[p][3]);
+          else *reinterpret_cast<uint2*>(dst) = make_uint2(pl[p][0], pl[p][1]);
+        }
+      }
     }
   }
 }
@@ -358,10 +405,10 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw)
       mbar_wait(&S.empty[st], ((it / kSStages) & 1) ^ 1, err, kErrEmptyWait);
       TRACE(2, it);
       StageBuf& T = S.stage[st];
-      if (U.bits == 1) build_table_pow2<1, XF32>(T, J.xa, U);
-      else if (U.bits == 2) build_table_pow2<2, XF32>(T, J.xa, U);
+      if (U.bits == 1) build_table_i8<1, XF32>(T, J.xa, U);
+      else if (U.bits == 2) build_table_i8<2, XF32>(T, J.xa, U);
       else if (U.bits == 3) build_table_b3<XF32>(T, J.xa, U);
-      else build_table_pow2<4, XF32>(T, J.xa, U);
+      else build_table_i8<4, XF32>(T, J.xa, U);
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.full[st]);
       TRACE(3, it);
@@ -370,20 +417,6 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw)
 }
 
 // ---- consumers --------------------------------------------------------------------------
-template <int B>
-struct SFmt {
-  static constexpr int kEps = 32 / B;
-  static constexpr int kPairs = kEps / 2;
-  static constexpr int kPos = 10 / B;
-  static constexpr int kMma = kEps / 4;
-  static constexpr uint32_t kMask = ((1u << B) - 1u) * 0x00010001u;
-  // fp16x2 operand number q of a word: codes q (low half) and q + eps/2 (high half), in place
-  __device__ static __forceinline__ uint32_t operand(uint32_t w, int q) {
-    const int stage = q / kPos, jj = q % kPos;
-    return (w >> (stage * kPos * B)) & (kMask << (B * jj));
-  }
-};
-
 __device__ __forceinline__ void apply_group(const StageBuf& Sg, int gu, int col, float xs, const float (&acc)[2][4],
                                             int p, float (&vs)[2][4]) {
   const uint2 sr = *reinterpret_cast<const uint2*>(&Sg.scales[gu][col]);
@@ -416,55 +449,101 @@ constexpr int kConsumerGroups = 2;
 constexpr int kGroupWarps = kSConsumers / kConsumerGroups;
 constexpr int kRowsPerWarp = kUnitRows / (kGroupWarps / 4);  // 32
 
+__device__ __forceinline__ void mma16832u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // Rows [32*kp, 32*kp+32) of the unit, columns of strip cw chunk ch; adds into vs.
+// B-operand lane group g feeds MMA column g: digit plane g & 3 (plane 3 is empty) of the even
+// (g < 4) or odd (g >= 4) group of the current pair of groups; rows of the other group see zeros.
 template <int B>
-__device__ __forceinline__ void consume_pow2(const StageBuf& Sg, const uint32_t* zero_row, int nrows, int ng, int cw,
-                                             int kp, float (&vs)[2][4]) {
-  using F = SFmt<B>;
+__device__ __forceinline__ void consume_i8(const StageBuf& Sg, const uint32_t* zero_row, int nrows, int ng, int cw,
+                                           int kp, float (&vs)[2][4]) {
+  using F = I8Fmt<B>;
+  constexpr int CPB = F::kCpb;
   constexpr int NI = kRowsPerWarp / 4;        // loop iterations: 4 word rows (one per c) each
-  constexpr int GPH = kRowsPerWarp / (4 * B); // groups inside this warp's rows = MMA columns in use
+  constexpr int GPH = kRowsPerWarp / (4 * B); // groups inside this warp's rows
+  constexpr int CH = B == 1 ? 2 : 4;          // word loads in flight (register budget)
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int ch = lane_chunk(B, g);
   const int r0 = kRowsPerWarp * kp;
-  float acc[2][4];
+  const bool plane_on = (g & 3) < 3;
+  const uint32_t* tp = Sg.tab + (g & 3) * F::kPlaneStride;
+  const int delta = g >> 2;
+  int acc[2][4];
 #pragma unroll
   for (int s = 0; s < 2; ++s)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[s][e] = 0.f;
+    for (int e = 0; e < 4; ++e) acc[s][e] = 0;
 #pragma unroll
-  for (int i0 = 0; i0 < NI; i0 += 4) {
-    uint4 w4[4];
+  for (int i0 = 0; i0 < NI; i0 += CH) {
+    uint4 w4[CH];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < CH; ++i)
       if (r0 + 4 * (i0 + i) < nrows) w4[i] = *strip_word(Sg, cw, r0 + 4 * (i0 + i) + c, ch);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (r0 + 4 * (i0 + i) < nrows) {
-        const int row = r0 + 4 * (i0 + i) + c;
-        const uint32_t* bp = (g == (i0 + i) / B) ? Sg.tab + row * F::kPairs : zero_row;
-        uint32_t bf[F::kPairs];
+    for (int i = 0; i < CH; ++i) {
+      const int it = i0 + i;
+      if (r0 + 4 * it < nrows) {
+        const int row = r0 + 4 * it + c;
+        const uint32_t* bp = (plane_on && delta == ((it / B) & 1)) ? tp + row * CPB : zero_row;
+        uint32_t bf[CPB];
+        if (CPB >= 4) {
 #pragma unroll
-        for (int q4 = 0; q4 < F::kPairs / 4; ++q4) {
-          const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
-          bf[4 * q4 + 0] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
+          for (int q4 = 0; q4 < CPB / 4; ++q4) {
+            const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
+            bf[4 * q4 + 0] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
+          }
+        } else {
+          const uint2 t = *reinterpret_cast<const uint2*>(bp);
+          bf[0] = t.x; bf[1] = t.y;
         }
         const uint32_t wv[4] = {w4[i].x, w4[i].y, w4[i].z, w4[i].w};
 #pragma unroll
-        for (int m = 0; m < F::kMma; ++m)
+        for (int m = 0; m < CPB / 2; ++m)
 #pragma unroll
           for (int s = 0; s < 2; ++s)
-            mma16816s(acc[s], F::operand(wv[2 * s], 2 * m), F::operand(wv[2 * s + 1], 2 * m),
-                      F::operand(wv[2 * s], 2 * m + 1), F::operand(wv[2 * s + 1], 2 * m + 1), bf[2 * m],
-                      bf[2 * m + 1]);
+            mma16832u8s8(acc[s], F::operand(wv[2 * s], 2 * m), F::operand(wv[2 * s + 1], 2 * m),
+                         F::operand(wv[2 * s], 2 * m + 1), F::operand(wv[2 * s + 1], 2 * m + 1), bf[2 * m],
+                         bf[2 * m + 1]);
+      }
+      if ((it + 1) % F::kWin == 0) {
+        // C columns 2c, 2c+1 carry digit planes 2(c&1), 2(c&1)+1 of group (c >> 1) of this pair
+        const int gu = kp * GPH + (it / F::kWin) * 2 + (c >> 1);
+        if (gu < ng) {
+          const int col = 32 * cw + 4 * ch;
+          const uint2 sr = *reinterpret_cast<const uint2*>(&Sg.scales[gu][col]);
+          const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sr.x));
+          const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sr.y));
+          const float f0 = Sg.fin[gu] * ((c & 1) ? 65536.0f : 1.0f), f1 = f0 * 256.0f;
+          // planes 0+1 (or 2 alone: plane 3 is empty) of one output column, then the scale
+          const float t00 = fmaf(f1, __int2float_rn(acc[0][1]), f0 * __int2float_rn(acc[0][0]));
+          const float t01 = fmaf(f1, __int2float_rn(acc[0][3]), f0 * __int2float_rn(acc[0][2]));
+          const float t10 = fmaf(f1, __int2float_rn(acc[1][1]), f0 * __int2float_rn(acc[1][0]));
+          const float t11 = fmaf(f1, __int2float_rn(acc[1][3]), f0 * __int2float_rn(acc[1][2]));
+          vs[0][0] = fmaf(s01.x, t00, vs[0][0]);
+          vs[0][2] = fmaf(s01.y, t01, vs[0][2]);
+          vs[1][0] = fmaf(s23.x, t10, vs[1][0]);
+          vs[1][2] = fmaf(s23.y, t11, vs[1][2]);
+          if ((c & 1) == 0) {  // the offset term z * sum(x), once per group and column
+            const uint2 zr = *reinterpret_cast<const uint2*>(&Sg.zeros[gu][col]);
+            const float2 z01 = __half22float2(*reinterpret_cast<const __half2*>(&zr.x));
+            const float2 z23 = __half22float2(*reinterpret_cast<const __half2*>(&zr.y));
+            const float xs = Sg.xsum[gu];
+            vs[0][1] = fmaf(z01.x, xs, vs[0][1]); vs[0][3] = fmaf(z01.y, xs, vs[0][3]);
+            vs[1][1] = fmaf(z23.x, xs, vs[1][1]); vs[1][3] = fmaf(z23.y, xs, vs[1][3]);
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[s][e] = 0;
       }
     }
-  }
-  // C column 2c+p carries group 2c+p of this row half
-#pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    const int d = 2 * c + p;
-    const int gu = kp * GPH + d;
-    if (d < GPH && gu < ng) apply_group(Sg, gu, 32 * cw + 4 * ch, Sg.xsum[gu], acc, p, vs);
   }
 }
 
@@ -555,10 +634,10 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
       mbar_wait(&S.full[st], (it / kSStages) & 1, err, kErrFullWait);
       if (wl == 0) TRACE(4 + grp, it >> 1);
       if (strip_on && kRowsPerWarp * kp < nrows) {
-        if (I.bits == 1) consume_pow2<1>(B, S.zero_row, nrows, ng, cw, kp, vs);
-        else if (I.bits == 2) consume_pow2<2>(B, S.zero_row, nrows, ng, cw, kp, vs);
+        if (I.bits == 1) consume_i8<1>(B, S.zero_row, nrows, ng, cw, kp, vs);
+        else if (I.bits == 2) consume_i8<2>(B, S.zero_row, nrows, ng, cw, kp, vs);
         else if (I.bits == 3) consume_b3(B, S.zero_row, nrows, ng, cw, kp, vs);
-        else consume_pow2<4>(B, S.zero_row, nrows, ng, cw, kp, vs);
+        else consume_i8<4>(B, S.zero_row, nrows, ng, cw, kp, vs);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.empty[st]);
