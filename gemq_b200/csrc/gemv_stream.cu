@@ -35,6 +35,7 @@ constexpr int kWarpFinisher = kWarpTable + kTableWarps;
 constexpr int kSWarps = kWarpFinisher + 1;
 constexpr int kSThreads = 32 * kSWarps;
 constexpr int kSStages = 4;
+constexpr int kTabSlots = 6;
 constexpr int kRedSlots = 4;
 constexpr int kUnitRows = 64;
 constexpr int kStripBytes = kUnitRows * 128;  // one TMA box: 64 word rows x 32 columns, 128B-swizzled
@@ -43,7 +44,7 @@ constexpr int kErrSlot = kMaxCounters - 1;  // last counter word holds the error
 
 #ifdef GEMQ_STREAM_TRACE
 // Development aid: nanosecond stamps of one CTA's roles (compiled out of the product build).
-__device__ unsigned long long g_trace[8][256];
+__device__ unsigned long long g_trace[10][256];
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -54,15 +55,21 @@ __device__ __forceinline__ unsigned long long gtime() {
 #define TRACE(row, i) do { } while (0)
 #endif
 
-enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrRedFullWait = 3, kErrRedEmptyWait = 4 };
+enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrRedFullWait = 3, kErrRedEmptyWait = 4, kErrTabFullWait = 5, kErrTabEmptyWait = 6 };
 
 struct StageBuf {
   alignas(1024) unsigned char words[4 * kStripBytes];
   alignas(16) __half scales[kMaxUnitGroups][128];
   alignas(16) __half zeros[kMaxUnitGroups][128];
+};
+
+// Activation operand table of one unit.  The tables sit in a ring of their own, deeper than the
+// data ring, so that building one (a few hundred dependent instructions on a single warp that
+// shares its scheduler with four busy consumer warps) is never on the refill path of a stage.
+struct TableBuf {
   // 1/2/4-bit: [3 digit planes][64 rows][8/B words of s8 digits], planes padded apart (kPlaneStride);
   // 3-bit: [2 variants][64 rows][16 halves]
-  alignas(16) uint32_t tab[2048 + 64];
+  alignas(16) uint32_t tab[1536 + 16];
   float xsum[kMaxUnitGroups];       // sum of the activations of each group
   float fin[kMaxUnitGroups];        // power of two that undoes the operand scaling of each group
 };
@@ -79,9 +86,11 @@ struct Range {
 
 struct StreamSmem {
   StageBuf stage[kSStages];
+  TableBuf table[kTabSlots];
   alignas(16) float red[kRedSlots][4][128];
   alignas(16) uint32_t zero_row[16];
-  alignas(8) unsigned long long full[kSStages], empty[kSStages], redfull[kRedSlots], redempty[kRedSlots];
+  alignas(8) unsigned long long full[kSStages], empty[kSStages], tfull[kTabSlots], tempty[kTabSlots], redfull[kRedSlots],
+      redempty[kRedSlots];
   JobInfo info[kMaxJobs];
   Range ranges[kMaxJobs];
   int n_ranges;
@@ -241,7 +250,7 @@ __device__ __forceinline__ int scale_exponent(float mx) {
 // word collects the codes {y * 8/B + q : y = 0..3}, all at position pos = B*q.  One AND per
 // four codes, no shifts.
 // The activations of a group are scaled by 2^(c - pos) so that the largest lies in
-// [2^22, 2^23), rounded to an integer and split into three balanced base-256 digits
+// [2^20, 2^21), rounded to an integer and split into three balanced base-256 digits
 // (each in [-128, 127]).  Digit plane pl of the table is an s8 B operand worth 256^pl; the
 // planes of two consecutive groups occupy MMA columns 0..2 and 4..6.  The integer
 // accumulation is exact.  (mma.sync with e4m3 operands would need half as many planes, but
@@ -256,16 +265,21 @@ struct I8Fmt {
   __device__ static __forceinline__ uint32_t operand(uint32_t w, int q) { return w & (kMask << (B * q)); }
 };
 
-// c = 22 - floor(log2(max|x|)) of a group: the largest scaled value lands in [2^22, 2^23).
+// c = 20 - floor(log2(max|x|)) of a group: the largest scaled value lands in [2^20, 2^21).
 __device__ __forceinline__ int scale_exponent_i8(float mx) {
-  int c = 22 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
-  return c < -15 ? -15 : (c > 60 ? 60 : c);
+  int c = 20 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
+  return c < -60 ? -60 : (c > 60 ? 60 : c);
 }
+
+// Rounds v (|v| < 2^21) to an integer iv and returns a word whose bytes 0 and 1 are the two low
+// balanced digits of iv plus 128 and whose byte 2 is 64 plus the top digit: adding
+// 1.5 * 2^23 + 0x8080 leaves iv + 0x8080 in the low mantissa bits.
+__device__ __forceinline__ uint32_t digits_word(float x, float f) { return __float_as_uint(fmaf(x, f, 12615808.0f)); }
 
 // Lane handles word rows `lane` and `lane + 32`.  A group is 4*B consecutive rows, so its
 // maximum and sum are reductions over 4*B neighbouring lanes.
 template <int B, bool XF32>
-__device__ __forceinline__ void build_table_i8(StageBuf& T, const void* x, const Unit& U) {
+__device__ __forceinline__ void build_table_i8(TableBuf& T, const void* x, const Unit& U) {
   using F = I8Fmt<B>;
   constexpr int EPS = 32 / B, CPB = F::kCpb, LPG = 4 * B;
   const int lane = threadIdx.x & 31;
@@ -323,17 +337,15 @@ __device__ __forceinline__ void build_table_i8(StageBuf& T, const void* x, const
         for (int qq = 0; qq < QB; ++qq) {
           const int q = q0 + qq;
           const float f = fb * (1.0f / static_cast<float>(1 << (B * q)));
-          int d0[4], d1[4], d2[4];
+          uint32_t e[4];
 #pragma unroll
-          for (int y = 0; y < 4; ++y) {
-            d0[y] = __float2int_rn(xv[y * CPB + q] * f);
-            d1[y] = (d0[y] + 128) >> 8;
-            d2[y] = (d1[y] + 128) >> 8;
-          }
-          // the low bytes of the four values of each digit, one per operand byte
-          pl[0][qq] = __byte_perm(__byte_perm(d0[0], d0[1], 0x0040), __byte_perm(d0[2], d0[3], 0x0040), 0x5410);
-          pl[1][qq] = __byte_perm(__byte_perm(d1[0], d1[1], 0x0040), __byte_perm(d1[2], d1[3], 0x0040), 0x5410);
-          pl[2][qq] = __byte_perm(__byte_perm(d2[0], d2[1], 0x0040), __byte_perm(d2[2], d2[3], 0x0040), 0x5410);
+          for (int y = 0; y < 4; ++y) e[y] = digits_word(xv[y * CPB + q], f);
+          // digit d of the four values goes to byte y of plane word d
+          const uint32_t x01 = __byte_perm(e[0], e[1], 0x5410), x23 = __byte_perm(e[2], e[3], 0x5410);
+          pl[0][qq] = __byte_perm(x01, x23, 0x6420) ^ 0x80808080u;
+          pl[1][qq] = __byte_perm(x01, x23, 0x7531) ^ 0x80808080u;
+          const uint32_t t = __byte_perm(__byte_perm(e[0], e[1], 0x0062), __byte_perm(e[2], e[3], 0x0062), 0x5410) ^ 0x40404040u;
+          pl[2][qq] = t | ((t & 0x40404040u) << 1);  // sign-extend the 7-bit top digit
         }
 #pragma unroll
         for (int p = 0; p < 3; ++p) {
@@ -348,7 +360,7 @@ __device__ __forceinline__ void build_table_i8(StageBuf& T, const void* x, const
 
 // 3-bit: element-wise, one group (128 elements, 4 per lane) at a time.
 template <bool XF32>
-__device__ __forceinline__ void build_table_b3(StageBuf& T, const void* x, const Unit& U) {
+__device__ __forceinline__ void build_table_b3(TableBuf& T, const void* x, const Unit& U) {
   const int lane = threadIdx.x & 31;
   uint4* z4 = reinterpret_cast<uint4*>(T.tab);
 #pragma unroll
@@ -401,23 +413,23 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw)
       if (it % kTableWarps != tw) continue;  // a single warp is latency-bound at about one unit per microsecond
       Unit U;
       make_unit(J, I, Pt.job, sl, Pt.chunk, U);
-      const int st = it % kSStages;
-      mbar_wait(&S.empty[st], ((it / kSStages) & 1) ^ 1, err, kErrEmptyWait);
+      const int ts = it % kTabSlots;
+      mbar_wait(&S.tempty[ts], ((it / kTabSlots) & 1) ^ 1, err, kErrTabEmptyWait);
       TRACE(2, it);
-      StageBuf& T = S.stage[st];
+      TableBuf& T = S.table[ts];
       if (U.bits == 1) build_table_i8<1, XF32>(T, J.xa, U);
       else if (U.bits == 2) build_table_i8<2, XF32>(T, J.xa, U);
       else if (U.bits == 3) build_table_b3<XF32>(T, J.xa, U);
       else build_table_i8<4, XF32>(T, J.xa, U);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&S.full[st]);
+      if (lane == 0) mbar_arrive(&S.tfull[ts]);
       TRACE(3, it);
     }
   }
 }
 
 // ---- consumers --------------------------------------------------------------------------
-__device__ __forceinline__ void apply_group(const StageBuf& Sg, int gu, int col, float xs, const float (&acc)[2][4],
+__device__ __forceinline__ void apply_group(const StageBuf& Sg, const TableBuf& Tb, int gu, int col, float xs, const float (&acc)[2][4],
                                             int p, float (&vs)[2][4]) {
   const uint2 sr = *reinterpret_cast<const uint2*>(&Sg.scales[gu][col]);
   const uint2 zr = *reinterpret_cast<const uint2*>(&Sg.zeros[gu][col]);
@@ -425,7 +437,7 @@ __device__ __forceinline__ void apply_group(const StageBuf& Sg, int gu, int col,
   const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sr.y));
   const float2 z01 = __half22float2(*reinterpret_cast<const __half2*>(&zr.x));
   const float2 z23 = __half22float2(*reinterpret_cast<const __half2*>(&zr.y));
-  const float fin = Sg.fin[gu];
+  const float fin = Tb.fin[gu];
   vs[0][p] += fmaf(s01.x * fin, acc[0][p], z01.x * xs);
   vs[0][2 + p] += fmaf(s01.y * fin, acc[0][2 + p], z01.y * xs);
   vs[1][p] += fmaf(s23.x * fin, acc[1][p], z23.x * xs);
@@ -461,7 +473,7 @@ __device__ __forceinline__ void mma16832u8s8(int (&d)[4], uint32_t a0, uint32_t 
 // B-operand lane group g feeds MMA column g: digit plane g & 3 (plane 3 is empty) of the even
 // (g < 4) or odd (g >= 4) group of the current pair of groups; rows of the other group see zeros.
 template <int B>
-__device__ __forceinline__ void consume_i8(const StageBuf& Sg, const uint32_t* zero_row, int nrows, int ng, int cw,
+__device__ __forceinline__ void consume_i8(const StageBuf& Sg, const TableBuf& Tb, const uint32_t* zero_row, int nrows, int ng, int cw,
                                            int kp, float (&vs)[2][4]) {
   using F = I8Fmt<B>;
   constexpr int CPB = F::kCpb;
@@ -472,7 +484,7 @@ __device__ __forceinline__ void consume_i8(const StageBuf& Sg, const uint32_t* z
   const int ch = lane_chunk(B, g);
   const int r0 = kRowsPerWarp * kp;
   const bool plane_on = (g & 3) < 3;
-  const uint32_t* tp = Sg.tab + (g & 3) * F::kPlaneStride;
+  const uint32_t* tp = Tb.tab + (g & 3) * F::kPlaneStride;
   const int delta = g >> 2;
   int acc[2][4];
 #pragma unroll
@@ -519,7 +531,7 @@ __device__ __forceinline__ void consume_i8(const StageBuf& Sg, const uint32_t* z
           const uint2 sr = *reinterpret_cast<const uint2*>(&Sg.scales[gu][col]);
           const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sr.x));
           const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sr.y));
-          const float f0 = Sg.fin[gu] * ((c & 1) ? 65536.0f : 1.0f), f1 = f0 * 256.0f;
+          const float f0 = Tb.fin[gu] * ((c & 1) ? 65536.0f : 1.0f), f1 = f0 * 256.0f;
           // planes 0+1 (or 2 alone: plane 3 is empty) of one output column, then the scale
           const float t00 = fmaf(f1, __int2float_rn(acc[0][1]), f0 * __int2float_rn(acc[0][0]));
           const float t01 = fmaf(f1, __int2float_rn(acc[0][3]), f0 * __int2float_rn(acc[0][2]));
@@ -533,7 +545,7 @@ __device__ __forceinline__ void consume_i8(const StageBuf& Sg, const uint32_t* z
             const uint2 zr = *reinterpret_cast<const uint2*>(&Sg.zeros[gu][col]);
             const float2 z01 = __half22float2(*reinterpret_cast<const __half2*>(&zr.x));
             const float2 z23 = __half22float2(*reinterpret_cast<const __half2*>(&zr.y));
-            const float xs = Sg.xsum[gu];
+            const float xs = Tb.xsum[gu];
             vs[0][1] = fmaf(z01.x, xs, vs[0][1]); vs[0][3] = fmaf(z01.y, xs, vs[0][3]);
             vs[1][1] = fmaf(z23.x, xs, vs[1][1]); vs[1][3] = fmaf(z23.y, xs, vs[1][3]);
           }
@@ -556,7 +568,7 @@ struct S3Fmt {
   }
 };
 
-__device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* zero_row, int nrows, int ng, int cw,
+__device__ __forceinline__ void consume_b3(const StageBuf& Sg, const TableBuf& Tb, const uint32_t* zero_row, int nrows, int ng, int cw,
                                            int kp, float (&vs)[2][4]) {
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int r0 = kRowsPerWarp * kp;
@@ -579,8 +591,8 @@ __device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* z
         mw[r][2] = S3Fmt::merge(w.z); mw[r][3] = S3Fmt::merge(w.w);
         const int d0 = (row * 10) >> 7;
         const uint32_t* bp = zero_row;
-        if (g == d0) bp = Sg.tab + row * 8;
-        else if (g == d0 + 1) bp = Sg.tab + 512 + row * 8;
+        if (g == d0) bp = Tb.tab + row * 8;
+        else if (g == d0 + 1) bp = Tb.tab + 512 + row * 8;
         const uint4 t4 = *reinterpret_cast<const uint4*>(bp);
         bf[5 * r + 0] = t4.x; bf[5 * r + 1] = t4.y; bf[5 * r + 2] = t4.z; bf[5 * r + 3] = t4.w;
         bf[5 * r + 4] = bp[4];
@@ -602,7 +614,7 @@ __device__ __forceinline__ void consume_b3(const StageBuf& Sg, const uint32_t* z
   for (int p = 0; p < 2; ++p) {
     const int d = 2 * c + p;  // unit-local group carried by C column d
     // groups are not aligned to the row halves: the offset term is added once, by half 0
-    if (d < 5 && d < ng) apply_group(Sg, d, 32 * cw + 4 * g, kp == 0 ? Sg.xsum[d] : 0.f, acc, p, vs);  // chunk = g
+    if (d < 5 && d < ng) apply_group(Sg, Tb, d, 32 * cw + 4 * g, kp == 0 ? Tb.xsum[d] : 0.f, acc, p, vs);  // chunk = g
   }
 }
 
@@ -630,17 +642,24 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
       const int ng = min(I.groups_per_unit, I.ngroups - sl * I.groups_per_unit);
       const int nrows = I.bits == 3 ? min(kUnitRows, I.kw - sl * kUnitRows) : ng * (4 * I.bits);
       const int st = it % kSStages;
+      const int ts = it % kTabSlots;
       const StageBuf& B = S.stage[st];
+      const TableBuf& T = S.table[ts];
+      mbar_wait(&S.tfull[ts], (it / kTabSlots) & 1, err, kErrTabFullWait);
       mbar_wait(&S.full[st], (it / kSStages) & 1, err, kErrFullWait);
       if (wl == 0) TRACE(4 + grp, it >> 1);
       if (strip_on && kRowsPerWarp * kp < nrows) {
-        if (I.bits == 1) consume_i8<1>(B, S.zero_row, nrows, ng, cw, kp, vs);
-        else if (I.bits == 2) consume_i8<2>(B, S.zero_row, nrows, ng, cw, kp, vs);
-        else if (I.bits == 3) consume_b3(B, S.zero_row, nrows, ng, cw, kp, vs);
-        else consume_i8<4>(B, S.zero_row, nrows, ng, cw, kp, vs);
+        if (I.bits == 1) consume_i8<1>(B, T, S.zero_row, nrows, ng, cw, kp, vs);
+        else if (I.bits == 2) consume_i8<2>(B, T, S.zero_row, nrows, ng, cw, kp, vs);
+        else if (I.bits == 3) consume_b3(B, T, S.zero_row, nrows, ng, cw, kp, vs);
+        else consume_i8<4>(B, T, S.zero_row, nrows, ng, cw, kp, vs);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&S.empty[st]);
+      if (wl == 0) TRACE(8 + grp, it >> 1);
+      if (lane == 0) {
+        mbar_arrive(&S.empty[st]);
+        mbar_arrive(&S.tempty[ts]);
+      }
     }
     // end of the part: sum the 8 MMA columns (= groups) and hand the strip to the finisher
 #pragma unroll
@@ -790,8 +809,12 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   int* err = P.counters + kErrSlot;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSStages; ++s) {
-      mbar_init(&S.full[s], 2);  // producer (with the byte count) + table warp
+      mbar_init(&S.full[s], 1);             // producer, with the byte count
       mbar_init(&S.empty[s], kGroupWarps);  // only the group that owns the unit releases its stage
+    }
+    for (int s = 0; s < kTabSlots; ++s) {
+      mbar_init(&S.tfull[s], 1);            // the table warp that built it
+      mbar_init(&S.tempty[s], kGroupWarps);
     }
     for (int s = 0; s < kRedSlots; ++s) {
       mbar_init(&S.redfull[s], kSConsumers);
