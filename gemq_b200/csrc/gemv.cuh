@@ -73,6 +73,10 @@ struct alignas(64) GemvParams {
   int comb_weighted;
   int epi;         // kEpi* (persistent kernel)
   int x_f32;       // activations are fp32 vectors (persistent kernel, e.g. h from the up-pair epilogue)
+  // The expert ids, bit widths and offsets the jobs point to were final before the previous
+  // kernel of the stream started: the persistent kernel may resolve them while that kernel
+  // still runs, ahead of its dependency wait.
+  int plan_early;
 };
 
 struct ResolvedJob {

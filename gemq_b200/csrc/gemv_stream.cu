@@ -51,7 +51,12 @@ __device__ __forceinline__ unsigned long long gtime() {
   return t;
 }
 #define TRACE(row, i) do { if (blockIdx.x == 70 && (threadIdx.x & 31) == 0 && (i) < 256) g_trace[row][i] = gtime(); } while (0)
+// per launch (ring of 64) and CTA: entry, dependencies resolved, roles start, end
+__device__ unsigned long long g_life[64][160][4];
+__device__ unsigned int g_life_id;
+#define LIFE(k) do { if (threadIdx.x == 0) g_life[life_id & 63][blockIdx.x][k] = gtime(); } while (0)
 #else
+#define LIFE(k) do { } while (0)
 #define TRACE(row, i) do { } while (0)
 #endif
 
@@ -151,13 +156,31 @@ struct PartWalk {
   }
 };
 
+// The launch parameters a plan lane needs.  They sit in the constant bank, cold at kernel
+// start, and do not depend on earlier kernels: they are read ahead of the dependency wait.
+struct PlanArgs {
+  const long long* idx;
+  const int* nbits;
+  const int* wq_strides;
+  const int* zs_strides;
+  int fixed_bits, N, K, map_base;
+};
+
+__device__ __forceinline__ void read_plan_args(const GemvParams& P, PlanArgs& A) {
+  const int lane = threadIdx.x & 31;
+  if (lane < P.n_jobs) {
+    const GemvJob& J = P.jobs[lane];
+    A.idx = J.idx; A.nbits = J.nbits; A.wq_strides = J.wq_strides; A.zs_strides = J.zs_strides;
+    A.fixed_bits = J.fixed_bits; A.N = J.N; A.K = J.K; A.map_base = J.map_base;
+  }
+}
+
 // Warp 0: one lane per job resolves the expert (two dependent global loads) and sizes the
 // job; a warp scan of the byte costs then gives this CTA its contiguous unit range per job.
-__device__ void make_plan(StreamSmem& S, const GemvParams& P) {
+__device__ void make_plan(StreamSmem& S, const GemvParams& P, const PlanArgs& J) {
   const int lane = threadIdx.x & 31;
   unsigned n_units = 0, unit_cost = 1;
   if (lane < P.n_jobs) {
-    const GemvJob& J = P.jobs[lane];
     const int e = J.idx ? static_cast<int>(*J.idx) : 0;
     const int bits = J.nbits ? J.nbits[e] : J.fixed_bits;
     JobInfo I;
@@ -172,7 +195,7 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P) {
     I.kw = cdiv(J.K, 32 / I.bits);
     S.info[lane] = I;
     Unit U;
-    make_unit(J, I, lane, I.slices - 1, 0, U);
+    make_unit(P.jobs[lane], I, lane, I.slices - 1, 0, U);
     const unsigned chunk_cost = (I.slices - 1) * (kUnitRows + I.groups_per_unit) + U.nrows + U.ng;  // x 512 B
     unit_cost = max(1u, chunk_cost / I.slices);
     n_units = static_cast<unsigned>(I.nch) * I.slices;
@@ -205,16 +228,19 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P) {
 // ---- producer ---------------------------------------------------------------------------
 __device__ void producer_role(StreamSmem& S, const GemvParams& P, int* err) {
   const int lane = threadIdx.x & 31;
+  TRACE(7, 5);
   PartWalk W;
   W.begin(S);
   Part Pt;
   int it = 0;
   while (W.next(S, Pt)) {
+    if (it == 0) TRACE(7, 6);
     const GemvJob& J = P.jobs[Pt.job];
     const JobInfo& I = S.info[Pt.job];
     for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
       Unit U;
       make_unit(J, I, Pt.job, sl, Pt.chunk, U);
+      if (it == 0) TRACE(7, 7);
       const int st = it % kSStages;
       const uint32_t par = (it / kSStages) & 1;
       StageBuf& B = S.stage[st];
@@ -806,6 +832,10 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   StreamSmem& S = *reinterpret_cast<StreamSmem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
+#ifdef GEMQ_STREAM_TRACE
+  const unsigned life_id = P.c_total == 0 ? 0u : static_cast<unsigned>(P.s_max >> 16);
+#endif
+  LIFE(0);
   int* err = P.counters + kErrSlot;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSStages; ++s) {
@@ -826,14 +856,29 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   if (warp == kWarpProducer && (threadIdx.x & 31) < kMaxMaps)  // descriptor fetch overlaps the plan
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(&P.maps[threadIdx.x & 31])) : "memory");
   // Let the next kernel of the stream start its own prologue as SMs free up, then wait until
-  // the previous kernel's results (expert ids, activations, zeroed workspace) are visible.
+  // the previous kernel's results (expert ids, activations, zeroed workspace) are visible.  The
+  // plan runs ahead of the wait when the launch says its inputs are older than that kernel.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  PlanArgs plan_args;
+  if (warp == 0) {
+    read_plan_args(P, plan_args);
+    if (P.plan_early) make_plan(S, P, plan_args);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  if (warp == 0) make_plan(S, P);
+  LIFE(1);
+  if (warp == 0) TRACE(7, 8);
+  if (warp == 1) TRACE(7, 11);
+  if (warp == 16) TRACE(7, 13);
+  if (warp == 0 && !P.plan_early) make_plan(S, P, plan_args);
+  LIFE(0);  // overwrites the entry stamp: plan done
+  if (warp == 0) TRACE(7, 9);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 0) TRACE(7, 10);
+  if (warp == 1) TRACE(7, 12);
   if (warp == 1) TRACE(7, 0);
   __syncthreads();
   if (warp == 1) TRACE(7, 1);
+  LIFE(2);
 #ifdef GEMQ_STREAM_TRACE
   if (blockIdx.x == 70 && threadIdx.x == 32) g_trace[7][3] = clock64();
 #endif
@@ -843,6 +888,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   else finisher_role(S, P, err);
   __syncthreads();
   if (warp == 1) TRACE(7, 2);
+  LIFE(3);
 #ifdef GEMQ_STREAM_TRACE
   if (blockIdx.x == 70 && threadIdx.x == 32) g_trace[7][4] = clock64();
 #endif
@@ -954,6 +1000,12 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
   P.c_total = cols;
   P.n_chunks = chunks;
   P.s_max = max_slices;
+#ifdef GEMQ_STREAM_TRACE
+  {
+    static int launch_id = 0;
+    P.s_max |= (launch_id++ & 0x7fff) << 16;
+  }
+#endif
   P.G = kGroup;
   P.partial = partial;
   P.counters = counters;
@@ -965,5 +1017,8 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
 #ifdef GEMQ_STREAM_TRACE
 extern "C" int gemq_debug_read_trace(unsigned long long* out) {
   return cudaMemcpyFromSymbol(out, gemq::g_trace, sizeof(gemq::g_trace)) == cudaSuccess ? 0 : -1;
+}
+extern "C" int gemq_debug_read_life(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, gemq::g_life, sizeof(gemq::g_life)) == cudaSuccess ? 0 : -1;
 }
 #endif

@@ -137,6 +137,7 @@ extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* o
     Q.n_jobs = nj;
     Q.epi = kEpiCombine;
     Q.x_f32 = 1;
+    Q.plan_early = 1;  // the ids were consumed by the up projection already; only h is new
     Q.comb_out = static_cast<__half*>(out) + static_cast<size_t>(t) * D;
     Q.comb_w = static_cast<const __half*>(w) + static_cast<size_t>(t) * A;
     Q.comb_weighted = A;
