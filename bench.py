@@ -420,7 +420,7 @@ def main():
             "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * D, "d2h_bytes_per_step": 2 * D},
             "gpu_launches": 3 * args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<false> (fused gate/up projection)",
+            "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel (fused gate/up projection)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": UP_KERNEL_DRAM_TRAFFIC,
                          "algorithmic_bytes_per_launch": up_alg, "avg_launch_us": up_avg_s * 1e6,

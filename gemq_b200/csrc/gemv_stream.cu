@@ -50,7 +50,7 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-#define TRACE(row, i) do { if (blockIdx.x == 70 && (threadIdx.x & 31) == 0 && (i) < 256) g_trace[row][i] = gtime(); } while (0)
+#define TRACE(row, i) do { if (!P.x_f32 && blockIdx.x == 70 && (threadIdx.x & 31) == 0 && (i) < 256) g_trace[row][i] = gtime(); } while (0)
 // per launch (ring of 64) and CTA: entry, dependencies resolved, roles start, end
 __device__ unsigned long long g_life[64][160][4];
 __device__ unsigned int g_life_id;
@@ -304,8 +304,8 @@ __device__ __forceinline__ uint32_t digits_word(float x, float f) { return __flo
 
 // Lane handles word rows `lane` and `lane + 32`.  A group is 4*B consecutive rows, so its
 // maximum and sum are reductions over 4*B neighbouring lanes.
-template <int B, bool XF32>
-__device__ __forceinline__ void build_table_i8(TableBuf& T, const void* x, const Unit& U) {
+template <int B>
+__device__ __forceinline__ void build_table_i8(TableBuf& T, const void* x, const Unit& U, bool XF32) {
   using F = I8Fmt<B>;
   constexpr int EPS = 32 / B, CPB = F::kCpb, LPG = 4 * B;
   const int lane = threadIdx.x & 31;
@@ -385,8 +385,7 @@ __device__ __forceinline__ void build_table_i8(TableBuf& T, const void* x, const
 }
 
 // 3-bit: element-wise, one group (128 elements, 4 per lane) at a time.
-template <bool XF32>
-__device__ __forceinline__ void build_table_b3(TableBuf& T, const void* x, const Unit& U) {
+__device__ __forceinline__ void build_table_b3(TableBuf& T, const void* x, const Unit& U, bool XF32) {
   const int lane = threadIdx.x & 31;
   uint4* z4 = reinterpret_cast<uint4*>(T.tab);
 #pragma unroll
@@ -425,8 +424,10 @@ __device__ __forceinline__ void build_table_b3(TableBuf& T, const void* x, const
   }
 }
 
-template <bool XF32>
+// One kernel serves fp16 and fp32 activations (a run-time branch in the table builders): the
+// gate/up and down launches of a layer then share their code in the instruction caches.
 __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw) {
+  const bool XF32 = P.x_f32 != 0;
   const int lane = threadIdx.x & 31;
   PartWalk W;
   W.begin(S);
@@ -443,10 +444,10 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw)
       mbar_wait(&S.tempty[ts], ((it / kTabSlots) & 1) ^ 1, err, kErrTabEmptyWait);
       TRACE(2, it);
       TableBuf& T = S.table[ts];
-      if (U.bits == 1) build_table_i8<1, XF32>(T, J.xa, U);
-      else if (U.bits == 2) build_table_i8<2, XF32>(T, J.xa, U);
-      else if (U.bits == 3) build_table_b3<XF32>(T, J.xa, U);
-      else build_table_i8<4, XF32>(T, J.xa, U);
+      if (U.bits == 1) build_table_i8<1>(T, J.xa, U, XF32);
+      else if (U.bits == 2) build_table_i8<2>(T, J.xa, U, XF32);
+      else if (U.bits == 3) build_table_b3(T, J.xa, U, XF32);
+      else build_table_i8<4>(T, J.xa, U, XF32);
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.tfull[ts]);
       TRACE(3, it);
@@ -711,14 +712,22 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
 
 // ---- finisher -----------------------------------------------------------------------------
 // Sum the partial slots of one job's chunk columns n..n+3 in slice order and restore them to zero.
-__device__ __forceinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J, int slices, int n) {
+// The loads go out in batches ahead of the zeroing stores, so that their latencies overlap.
+__device__ __noinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J, int slices, int n) {
+  constexpr int kBatch = 8;
   float* src = P.partial + J.col_base + n;
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < slices; ++s) {
-    float4* q = reinterpret_cast<float4*>(src + static_cast<size_t>(s) * P.c_total);
-    const float4 t = __ldcg(q);
-    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
-    __stcg(q, make_float4(0.f, 0.f, 0.f, 0.f));
+  for (int s0 = 0; s0 < slices; s0 += kBatch) {
+    float4 t[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (s0 + i < slices) t[i] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(s0 + i) * P.c_total));
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (s0 + i < slices) {
+        sum.x += t[i].x; sum.y += t[i].y; sum.z += t[i].z; sum.w += t[i].w;
+        __stcg(reinterpret_cast<float4*>(src + static_cast<size_t>(s0 + i) * P.c_total), make_float4(0.f, 0.f, 0.f, 0.f));
+      }
   }
   return sum;
 }
@@ -826,7 +835,6 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
   }
 }
 
-template <bool XF32>
 __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_constant__ GemvParams P) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   StreamSmem& S = *reinterpret_cast<StreamSmem*>(
@@ -884,7 +892,7 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
 #endif
   if (warp < kSConsumers) consumer_role(S, P, err);
   else if (warp == kWarpProducer) producer_role(S, P, err);
-  else if (warp < kWarpFinisher) table_role<XF32>(S, P, err, warp - kWarpTable);
+  else if (warp < kWarpFinisher) table_role(S, P, err, warp - kWarpTable);
   else finisher_role(S, P, err);
   __syncthreads();
   if (warp == 1) TRACE(7, 2);
@@ -920,14 +928,13 @@ static int sm_count() {
   return cached[dev];
 }
 
-template <bool XF32>
 static int launch_stream_t(GemvParams& P, cudaStream_t stream, int units_bound) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   const size_t smem = sizeof(StreamSmem) + 1024;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemv_stream_kernel<XF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return GEMQ_ERR_LAUNCH;
     attr_set[dev] = true;
@@ -947,7 +954,7 @@ static int launch_stream_t(GemvParams& P, cudaStream_t stream, int units_bound) 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel<XF32>, P) != cudaSuccess) return GEMQ_ERR_LAUNCH;
+  if (cudaLaunchKernelEx(&cfg, gemv_stream_kernel, P) != cudaSuccess) return GEMQ_ERR_LAUNCH;
   return launch_status();
 }
 
@@ -1009,7 +1016,7 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
   P.G = kGroup;
   P.partial = partial;
   P.counters = counters;
-  return P.x_f32 ? launch_stream_t<true>(P, stream, units) : launch_stream_t<false>(P, stream, units);
+  return launch_stream_t(P, stream, units);
 }
 
 }  // namespace gemq
