@@ -44,6 +44,7 @@ struct GemvJob {
   int tile_base;           // first blockIdx.x of this job
   int chunk_base;          // first arrival counter of this job (shared by the jobs of a finish group)
   int map_base;            // persistent kernel: index of this job's wq tensor map (+1 scales, +2 zeros)
+  int mask_base;           // persistent kernel: first counter word holding, per column chunk, the set of partial slots in use
   long long wq_rows;       // host: rows of the wq tensor (tensor-map extent)
   long long zs_rows;       // host: rows of the scales / zeros tensors
 };

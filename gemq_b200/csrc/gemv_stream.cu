@@ -209,8 +209,14 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P, const PlanArgs& J)
   }
   const unsigned total = __shfl_sync(0xffffffffu, incl, 31);
   const unsigned prefix = incl - w;
-  const unsigned lo = static_cast<unsigned>(static_cast<unsigned long long>(total) * blockIdx.x / gridDim.x);
-  const unsigned hi = static_cast<unsigned>(static_cast<unsigned long long>(total) * (blockIdx.x + 1) / gridDim.x);
+  unsigned lo, hi;
+  if (total < 0xffffffffu / (gridDim.x + 1)) {  // the usual case: no 64-bit division on the critical path
+    lo = total * blockIdx.x / gridDim.x;
+    hi = total * (blockIdx.x + 1) / gridDim.x;
+  } else {
+    lo = static_cast<unsigned>(static_cast<unsigned long long>(total) * blockIdx.x / gridDim.x);
+    hi = static_cast<unsigned>(static_cast<unsigned long long>(total) * (blockIdx.x + 1) / gridDim.x);
+  }
   unsigned ulo = lo <= prefix ? 0u : (lo - prefix + unit_cost - 1) / unit_cost;
   unsigned uhi = hi <= prefix ? 0u : (hi - prefix + unit_cost - 1) / unit_cost;
   ulo = min(ulo, n_units);
@@ -712,11 +718,37 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
 
 // ---- finisher -----------------------------------------------------------------------------
 // Sum the partial slots of one job's chunk columns n..n+3 in slice order and restore them to zero.
-// The loads go out in batches ahead of the zeroing stores, so that their latencies overlap.
-__device__ __noinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J, int slices, int n) {
-  constexpr int kBatch = 8;
+// A word per (job, chunk) records which slots hold a partial (one bit per part, at the part's
+// first slice): only those are read, a few at a time so that their latencies overlap.  Jobs
+// with more than 32 slices scan every slot.
+__device__ __noinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J, int slices, int chunk, int n) {
+  constexpr int kBatch = 4;
   float* src = P.partial + J.col_base + n;
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (slices <= 32) {
+    unsigned m = __ldcg(reinterpret_cast<const unsigned*>(P.counters + J.mask_base + chunk));
+    while (m) {
+      float4 t[kBatch];
+      float4* q[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        q[i] = nullptr;
+        if (m) {
+          const int s = __ffs(m) - 1;
+          m &= m - 1;
+          q[i] = reinterpret_cast<float4*>(src + static_cast<size_t>(s) * P.c_total);
+          t[i] = __ldcg(q[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i)
+        if (q[i]) {
+          sum.x += t[i].x; sum.y += t[i].y; sum.z += t[i].z; sum.w += t[i].w;
+          __stcg(q[i], make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+    }
+    return sum;
+  }
   for (int s0 = 0; s0 < slices; s0 += kBatch) {
     float4 t[kBatch];
 #pragma unroll
@@ -748,13 +780,13 @@ __device__ __forceinline__ float4 round_half4(const float4& v) {
 __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Part& Pt, int n) {
   if (P.epi == kEpiStore) {
     const GemvJob& J = P.jobs[Pt.job];
-    store_half4(J.y + n, drain_slots(P, J, S.info[Pt.job].slices, n));
+    store_half4(J.y + n, drain_slots(P, J, S.info[Pt.job].slices, Pt.chunk, n));
   } else if (P.epi == kEpiUpPair) {
     const int j1 = Pt.job & ~1, j3 = j1 + 1;
     const GemvJob& J1 = P.jobs[j1];
     const GemvJob& J3 = P.jobs[j3];
-    const float4 a = round_half4(drain_slots(P, J1, S.info[j1].slices, n));
-    const float4 b = round_half4(drain_slots(P, J3, S.info[j3].slices, n));
+    const float4 a = round_half4(drain_slots(P, J1, S.info[j1].slices, Pt.chunk, n));
+    const float4 b = round_half4(drain_slots(P, J3, S.info[j3].slices, Pt.chunk, n));
     if (J1.y) store_half4(J1.y + n, a);
     if (J3.y) store_half4(J3.y + n, b);
     if (J1.h)
@@ -764,7 +796,7 @@ __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Par
     float4 accw = make_float4(0.f, 0.f, 0.f, 0.f), res = accw;
     for (int i = 0; i < P.n_jobs; ++i) {
       const GemvJob& Ji = P.jobs[i];
-      const float4 x2 = round_half4(drain_slots(P, Ji, S.info[i].slices, n));
+      const float4 x2 = round_half4(drain_slots(P, Ji, S.info[i].slices, Pt.chunk, n));
       if (Ji.y) store_half4(Ji.y + n, x2);
       if (i < P.comb_weighted) {
         const float wgt = __half2float(P.comb_w[i]);
@@ -808,10 +840,9 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
       if (col_on) store_half4(J.y + n, r);
       continue;
     }
-    if (col_on) {
-      __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(Pt.sa) * P.c_total + J.col_base + n), r);
-      __threadfence();
-    }
+    if (col_on) __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(Pt.sa) * P.c_total + J.col_base + n), r);
+    if (lane == 0) atomicOr(reinterpret_cast<unsigned*>(P.counters + J.mask_base + Pt.chunk), 1u << (Pt.sa & 31));
+    __threadfence();
     __syncwarp();
     int last = 0;
     if (lane == 0) {
@@ -831,6 +862,12 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
     if (last) {
       __threadfence();
       if (col_on) finish_group(S, P, Pt, n);
+      __syncwarp();
+      if (lane == 0) {  // every lane has read the slot sets of the jobs it drained: clear them
+        const int j0 = P.epi == kEpiStore ? Pt.job : (P.epi == kEpiUpPair ? (Pt.job & ~1) : 0);
+        const int j1 = P.epi == kEpiStore ? Pt.job + 1 : (P.epi == kEpiUpPair ? j0 + 2 : P.n_jobs);
+        for (int j = j0; j < j1; ++j) P.counters[P.jobs[j].mask_base + Pt.chunk] = 0;
+      }
     }
   }
 }
@@ -878,7 +915,9 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   if (warp == 1) TRACE(7, 11);
   if (warp == 16) TRACE(7, 13);
   if (warp == 0 && !P.plan_early) make_plan(S, P, plan_args);
-  LIFE(0);  // overwrites the entry stamp: plan done
+#ifdef GEMQ_STREAM_TRACE
+  if (threadIdx.x == 0) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); g_life[life_id & 63][blockIdx.x][0] = smid; }
+#endif
   if (warp == 0) TRACE(7, 9);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 0) TRACE(7, 10);
@@ -1002,7 +1041,12 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
     units += nch * cdiv(J.K / kGroup, 16);     // at least this many (1-bit units: 16 groups)
   }
   if (P.epi == kEpiUpPair && (P.n_jobs & 1)) return GEMQ_ERR_BAD_ARG;
-  if (chunks >= kErrSlot) return GEMQ_ERR_WORKSPACE;
+  int words = chunks;  // arrival counters, then one slot-set word per job and column chunk
+  for (int i = 0; i < P.n_jobs; ++i) {
+    P.jobs[i].mask_base = words;
+    words += cdiv(P.jobs[i].N, 128);
+  }
+  if (words >= kErrSlot) return GEMQ_ERR_WORKSPACE;
   if (static_cast<size_t>(max_slices) * cols > partial_floats) return GEMQ_ERR_WORKSPACE;
   P.c_total = cols;
   P.n_chunks = chunks;
