@@ -5,14 +5,21 @@
 //   down kernel : Ys[r, :] = (H[r, :] @ deq(w2[e])) * routing weight
 //   combine     : out[t]   = sum over the token's experts, in expert order (index_add_ semantics)
 //
-// One CTA computes a 128 (rows) x 128 (output columns) tile.  A 3-stage mbarrier ring feeds
-// tcgen05.mma (kind::f16, M=128, N=128, K=16 per instruction, fp32 accumulators in TMEM):
-//   * warp 4 loads the activation tile with tiled TMA (128B swizzle, K-major);
-//   * warps 0-3 (one thread per output column) read the packed words of their column, de-quantise
-//     them with the reference's single-rounded fp16 fma (bit-exact weights), optionally convert to
-//     bf16, and write the K-major 128B-swizzled B tile straight into shared memory;
-//   * one thread of warp 5 issues the MMAs and commits stage releases;
-//   * warps 0-3 then read the accumulators back with tcgen05.ld and run the epilogue.
+// One CTA computes a 256 (rows) x 128 (output columns) tile of one expert, as two M=128
+// accumulators that share every de-quantised weight tile.  A 3-stage mbarrier ring over 64-wide
+// k-blocks feeds tcgen05.mma (kind::f16, M=128, N=128, K=16 per instruction, fp32 accumulators in
+// TMEM: 512 columns for the gate/up pass, 256 otherwise):
+//   * a TMA warp loads the activation tile (tiled TMA, 128B swizzle, K-major, box 64 x 256);
+//   * sixteen producer warps in two groups that take alternate k-blocks (one thread per output
+//     column and 32-element half of the k-block) read the packed words of their column two
+//     k-blocks ahead, de-quantise them with the reference's single-rounded fp16 fma (bit-exact
+//     weights: the code is extracted in place as the fp16 1024 + q and one hfma2 with the
+//     per-position constants 2^-pos and -1024 * 2^-pos gives q exactly), and write the K-major
+//     128B-swizzled B tile straight into shared memory; bf16 activations are converted to fp16
+//     when the rows are gathered, so the products stay in one format;
+//   * one thread of the MMA warp issues the MMAs and commits stage releases;
+//   * the producer warps then read the accumulators back with tcgen05.ld and run the epilogue
+//     (SiLU-gate product, routing weight, rounding to the activation type).
 // Expert of a row tile, its first row and its valid row count come from a tile table built on
 // the device, so the routing never reaches the host.  Every wait is bounded.
 #include "gemv.cuh"
@@ -24,13 +31,13 @@ constexpr int kGemmBM = 256, kGemmBN = 128, kGemmBK = 64;  // CTA tile; two M=12
 constexpr int kMmaM = 128;
 constexpr int kGemmStages = 3;
 constexpr int kGemmProducerWarps = 16;
-constexpr int kGemmThreads = 32 * (kGemmProducerWarps + 2);  // 8 de-quantise/epilogue warps + TMA warp + MMA warp
+constexpr int kGemmThreads = 32 * (kGemmProducerWarps + 2);  // de-quantise/epilogue warps + TMA warp + MMA warp
 constexpr int kTileBytes = kGemmBN * kGemmBK * 2;  // 16 KB: a B tile, or one 128-row half of the A tile
 
 enum { kErrGemmAFull = 11, kErrGemmBFull = 12, kErrGemmEmpty = 13, kErrGemmAcc = 14 };
 
 struct alignas(64) GemmParams {
-  CUtensorMap a_map;        // activations [rows, K] (16-bit), box 64 x 128, 128B swizzle
+  CUtensorMap a_map;        // activations [rows, K] (16-bit), box 64 x 256, 128B swizzle
   const uint32_t* wq[2];    // stacked packed words ([0] only unless UP)
   const __half* scales[2];
   const __half* zeros[2];
