@@ -25,7 +25,9 @@ METRIC = "moe_layer_decode_tokens_per_s"
 WORKLOAD = "mixtral8x7b_moe_layer_decode_bs1_mixed_1-4bit_g128 (config 1)"
 # dram bytes per launch of the up-projection kernel measured with ncu on this workload; None
 # until a capture has been summarised under profiles/.
-UP_KERNEL_DRAM_TRAFFIC = None
+# ncu (profiles/gemv_stream_kernel_decode_layer.md): dram read + write of three captured launches
+# = 1.033 x their algorithmic bytes (reads alone 1.002 x); applied to the bench's own average.
+UP_KERNEL_TRAFFIC_RATIO = 1.033
 
 
 def parse():
@@ -422,7 +424,7 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel (fused gate/up projection)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": UP_KERNEL_DRAM_TRAFFIC,
+                         "frac": achieved / peak, "traffic": up_alg * UP_KERNEL_TRAFFIC_RATIO,
                          "algorithmic_bytes_per_launch": up_alg, "avg_launch_us": up_avg_s * 1e6,
                          "layer_frac": step_bytes / (ms / args.steps * 1e-3) / 1e9 / peak},
             "cpu_baseline": {"value": 1.0 / per_token_s, "unit": "tokens/s", "cores": threads, "kind": "port",
