@@ -22,6 +22,8 @@
 //     (SiLU-gate product, routing weight, rounding to the activation type).
 // Expert of a row tile, its first row and its valid row count come from a tile table built on
 // the device, so the routing never reaches the host.  Every wait is bounded.
+#include <type_traits>
+
 #include "gemv.cuh"
 #include "ptx.cuh"
 
@@ -83,7 +85,7 @@ __device__ __forceinline__ uint32_t pack_act2(__half2 v) {
 // j + eps/2 of the word, in place); minus 1024 and times 2^-pos are exact, so the fma sees the
 // exact integer code.  A byte permute then pairs neighbouring k.
 template <bool BF16, int B>
-__device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int chunk0, const uint32_t (&w)[5],
+__device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int chunk0, const uint32_t* w,
                                                __half2 s2, __half2 z2) {
   constexpr int EPS = 32 / B, PAIRS = EPS / 2, NPOS = 10 / B, NW = 32 / EPS;
   constexpr uint32_t MASK = ((1u << B) - 1u) * 0x00010001u;
@@ -116,62 +118,128 @@ __device__ __forceinline__ void dequant32_pow2(unsigned char* brow, int swz, int
         make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
 }
 
-// 3-bit: 10 codes per word, the 32-element window is not word aligned: walk the codes.
+// 3-bit: 10 codes per word, so a 32-element window starts at an even code of its first word and
+// spans four words.  Per word: fold codes 5..9 into the upper half (code j and j + 5 now sit at
+// bit 3*(j % 5) of the two 16-bit halves), extract them in place like the other widths (positions
+// 9 and 12 after a shift by 9: the fp16 mantissa has 10 bits), and permute the (j, j + 5) pairs
+// into neighbouring-k pairs.  All 20 pairs of the four words are formed; the window is the 16
+// that start at pair (k0 mod 10) / 2.
 template <bool BF16>
-__device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int chunk0, const uint32_t (&w)[5], int k0,
+__device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int chunk0, const uint32_t* w, int k0,
                                              __half2 s2, __half2 z2) {
-  const int w0 = k0 / 10;
-  int wi = 0, j = k0 - w0 * 10;
-  uint32_t cur = w[0] >> (3 * j);
-  uint32_t outw[16];
-  const __half2 k1024 = __float2half2_rn(1024.f);
+  uint32_t pr[20];
 #pragma unroll
-  for (int p = 0; p < 16; ++p) {
-    uint32_t q2 = 0x64006400u;
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t m = (w[i] & 0x00007fffu) | ((w[i] << 1) & 0x7fff0000u);
+    const uint32_t mh = m >> 9;
+    uint32_t v[5];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      q2 |= (cur & 7u) << (16 * h);
-      cur >>= 3;
-      if (++j == 10) {
-        j = 0;
-        ++wi;
-        uint32_t nxt = 0;
+    for (int q = 0; q < 5; ++q) {
+      const int jj = q < 3 ? q : q - 3;
+      const uint32_t bits = ((q < 3 ? m : mh) & (0x00070007u << (3 * jj))) | 0x64006400u;
+      constexpr float kInv[3] = {1.f, 1.f / 8, 1.f / 64};
+      const float inv = kInv[jj];
+      const __half2 c = __hfma2(*reinterpret_cast<const __half2*>(&bits), __float2half2_rn(inv), __float2half2_rn(-1024.f * inv));
+      const __half2 d = __hfma2(c, s2, z2);
+      v[q] = *reinterpret_cast<const uint32_t*>(&d);
+    }
+    // v[q] = (code q, code q + 5)  ->  neighbouring codes
+    pr[5 * i + 0] = __byte_perm(v[0], v[1], 0x5410);  // codes 0, 1
+    pr[5 * i + 1] = __byte_perm(v[2], v[3], 0x5410);  // 2, 3
+    pr[5 * i + 2] = __byte_perm(v[4], v[0], 0x7610);  // 4, 5
+    pr[5 * i + 3] = __byte_perm(v[1], v[2], 0x7632);  // 6, 7
+    pr[5 * i + 4] = __byte_perm(v[3], v[4], 0x7632);  // 8, 9
+  }
+  if (BF16) {
 #pragma unroll
-        for (int i = 1; i < 5; ++i) nxt = (wi == i) ? w[i] : nxt;
-        cur = nxt;
+    for (int t = 0; t < 20; ++t) pr[t] = pack_act2<true>(*reinterpret_cast<const __half2*>(&pr[t]));
+  }
+  const int sh = (k0 % 10) >> 1;  // warp-uniform: all lanes of a warp share k0
+  auto store = [&](auto SH) {
+    constexpr int O = decltype(SH)::value;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      *reinterpret_cast<uint4*>(brow + (((chunk0 + c) ^ swz) << 4)) =
+          make_uint4(pr[O + 4 * c], pr[O + 4 * c + 1], pr[O + 4 * c + 2], pr[O + 4 * c + 3]);
+  };
+  switch (sh) {
+    case 0: store(std::integral_constant<int, 0>{}); break;
+    case 1: store(std::integral_constant<int, 1>{}); break;
+    case 2: store(std::integral_constant<int, 2>{}); break;
+    case 3: store(std::integral_constant<int, 3>{}); break;
+    default: store(std::integral_constant<int, 4>{}); break;
+  }
+}
+
+// ---- B producer loop, specialised for the expert's bit width --------------------------------
+// Thread = output column n0 + col and one 32-element half kh of a 64-wide k-block; the two
+// groups of 8 warps take alternate k-blocks.  Words and metadata are fetched two of the group's
+// k-blocks ahead (register ring of three sets), so the global-load latency is off the critical
+// path of the stage ring.  Everything that does not change along k (bit width, expert offsets,
+// words per window) is fixed outside the loop: the loop body is loads at constant strides, the
+// de-quantisation and one barrier arrival.
+template <bool UP, bool BF16, int B>
+__device__ __forceinline__ void produce_loop(GemmSmem& S, const GemmParams& P, int expert, int n0, int KB) {
+  constexpr int NMAT = UP ? 2 : 1;
+  constexpr int EPS = B == 3 ? 10 : 32 / B;
+  constexpr int NW = B == 3 ? 4 : 32 / EPS;  // words that cover a 32-element window (3-bit: 4 for every even start)
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int grp = tid >> 8, col = tid & 127, kh = (tid >> 7) & 1;
+  const size_t N = P.N;
+  const int ngroups = P.K / P.G;
+  const size_t woff = P.wq_strides ? static_cast<size_t>(P.wq_strides[expert]) : 0;
+  const size_t zoff = P.zs_strides ? static_cast<size_t>(P.zs_strides[expert]) : static_cast<size_t>(expert) * ngroups * N;
+  const int gshift = (P.G & (P.G - 1)) == 0 ? __ffs(P.G) - 1 : -1;
+  const uint32_t* wp[NMAT];
+  const __half* sp[NMAT];
+  const __half* zp[NMAT];
+#pragma unroll
+  for (int m = 0; m < NMAT; ++m) {
+    wp[m] = P.wq[m] + woff + n0 + col;
+    sp[m] = P.scales[m] + zoff + n0 + col;
+    zp[m] = P.zeros[m] + zoff + n0 + col;
+  }
+  struct WSet { uint32_t w[NMAT][NW]; __half sc[NMAT], zr[NMAT]; };
+  WSet ring[3];
+  auto fetch = [&](WSet& W, int kb) {
+    const int k0 = kb * kGemmBK + 32 * kh;
+    const int first = k0 / EPS;  // constant divisor
+    const int g = gshift >= 0 ? (kb * kGemmBK) >> gshift : (kb * kGemmBK) / P.G;
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) {
+      const uint32_t* q = wp[m] + static_cast<size_t>(first) * N;
+#pragma unroll
+      for (int i = 0; i < NW; ++i) W.w[m][i] = q[static_cast<size_t>(i) * N];
+      W.sc[m] = sp[m][static_cast<size_t>(g) * N];
+      W.zr[m] = zp[m][static_cast<size_t>(g) * N];
+    }
+  };
+  auto produce = [&](const WSet& W, int kb) {
+    const int s = kb % kGemmStages;
+    mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
+#pragma unroll
+    for (int m = 0; m < NMAT; ++m) {
+      const __half2 s2 = __half2half2(W.sc[m]), z2 = __half2half2(W.zr[m]);
+      unsigned char* brow = S.b[s][m] + col * 128;
+      if (B == 3) dequant32_b3<BF16>(brow, col & 7, 4 * kh, W.w[m], kb * kGemmBK + 32 * kh, s2, z2);
+      else dequant32_pow2<BF16, (B == 3 ? 2 : B)>(brow, col & 7, 4 * kh, W.w[m], s2, z2);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&S.b_full[s]);
+  };
+  if (grp < KB) fetch(ring[0], grp);
+  if (grp + 2 < KB) fetch(ring[1], grp + 2);
+  for (int kb0 = grp; kb0 < KB; kb0 += 6) {
+#pragma unroll
+    for (int u = 0; u < 3; ++u) {
+      const int kb = kb0 + 2 * u;
+      if (kb < KB) {
+        if (kb + 4 < KB) fetch(ring[(u + 2) % 3], kb + 4);
+        produce(ring[u], kb);
       }
     }
-    outw[p] = pack_act2<BF16>(__hfma2(__hsub2(*reinterpret_cast<const __half2*>(&q2), k1024), s2, z2));
   }
-#pragma unroll
-  for (int c = 0; c < 4; ++c)
-    *reinterpret_cast<uint4*>(brow + (((chunk0 + c) ^ swz) << 4)) =
-        make_uint4(outw[4 * c], outw[4 * c + 1], outw[4 * c + 2], outw[4 * c + 3]);
-}
-
-// Packed words of one column that cover the 32 reduction elements [k0, k0+32): at most 5.
-__device__ __forceinline__ void load_words32(uint32_t (&w)[5], const uint32_t* wcol, size_t N, int bits, int k0) {
-  int first, cnt;
-  if (bits == 3) {
-    first = k0 / 10;
-    cnt = (k0 + 31) / 10 - first + 1;
-  } else {
-    const int eps = 32 / bits;
-    first = k0 / eps;
-    cnt = 32 / eps;
-  }
-#pragma unroll
-  for (int i = 0; i < 5; ++i) w[i] = i < cnt ? wcol[static_cast<size_t>(first + i) * N] : 0u;
-}
-
-template <bool BF16>
-__device__ __forceinline__ void dequant32(unsigned char* brow, int swz, int chunk0, const uint32_t (&w)[5], int bits,
-                                          int k0, __half s, __half z) {
-  const __half2 s2 = __half2half2(s), z2 = __half2half2(z);
-  if (bits == 1) dequant32_pow2<BF16, 1>(brow, swz, chunk0, w, s2, z2);
-  else if (bits == 2) dequant32_pow2<BF16, 2>(brow, swz, chunk0, w, s2, z2);
-  else if (bits == 3) dequant32_b3<BF16>(brow, swz, chunk0, w, k0, s2, z2);
-  else dequant32_pow2<BF16, 4>(brow, swz, chunk0, w, s2, z2);
 }
 
 template <bool BF16>
@@ -238,51 +306,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   const uint32_t tmem = S.tmem_base;
 
   if (warp < kGemmProducerWarps) {
-    // ---- B producers: thread owns output column n0 + col and one 32-element half of the k-block --
-    // Two groups of 8 warps take alternate k-blocks, so twice as many warps hide the latencies of
-    // the de-quantisation chain.  Inside a group: one thread per column and 32-element half.
-    const int grp = tid >> 8, col = tid & 127, kh = (tid >> 7) & 1;
+    // ---- B producers ---------------------------------------------------------------------------
     const int bits = P.nbits ? P.nbits[expert] : P.fixed_bits;
-    const int ngroups = P.K / P.G;
-    const size_t woff = P.wq_strides ? static_cast<size_t>(P.wq_strides[expert]) : 0;
-    const size_t zoff = P.zs_strides ? static_cast<size_t>(P.zs_strides[expert])
-                                     : static_cast<size_t>(expert) * ngroups * P.N;
-    const size_t N = P.N;
-    // Words and metadata are fetched two k-blocks ahead (register ring of three sets), so the
-    // global-load latency is off the critical path of the stage ring.
-    struct WSet { uint32_t w[NMAT][5]; __half sc[NMAT], zr[NMAT]; };
-    WSet ring[3];
-    auto fetch = [&](WSet& W, int kb) {
-      const int k0 = kb * kGemmBK + 32 * kh, g = (kb * kGemmBK) / P.G;
-#pragma unroll
-      for (int m = 0; m < NMAT; ++m) {
-        load_words32(W.w[m], P.wq[m] + woff + n0 + col, N, bits, k0);
-        W.sc[m] = P.scales[m][zoff + static_cast<size_t>(g) * N + n0 + col];
-        W.zr[m] = P.zeros[m][zoff + static_cast<size_t>(g) * N + n0 + col];
-      }
-    };
-    auto produce = [&](const WSet& W, int kb) {
-      const int s = kb % kGemmStages;
-      mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
-#pragma unroll
-      for (int m = 0; m < NMAT; ++m)
-        dequant32<BF16>(S.b[s][m] + col * 128, col & 7, 4 * kh, W.w[m], bits, kb * kGemmBK + 32 * kh, W.sc[m], W.zr[m]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.b_full[s]);
-    };
-    if (grp < KB) fetch(ring[0], grp);
-    if (grp + 2 < KB) fetch(ring[1], grp + 2);
-    for (int kb0 = grp; kb0 < KB; kb0 += 6) {
-#pragma unroll
-      for (int u = 0; u < 3; ++u) {
-        const int kb = kb0 + 2 * u;
-        if (kb < KB) {
-          if (kb + 4 < KB) fetch(ring[(u + 2) % 3], kb + 4);
-          produce(ring[u], kb);
-        }
-      }
-    }
+    if (bits == 1) produce_loop<UP, BF16, 1>(S, P, expert, n0, KB);
+    else if (bits == 2) produce_loop<UP, BF16, 2>(S, P, expert, n0, KB);
+    else if (bits == 3) produce_loop<UP, BF16, 3>(S, P, expert, n0, KB);
+    else produce_loop<UP, BF16, 4>(S, P, expert, n0, KB);
     // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = tile rows -------------------------
     mbar_wait(&S.acc_full, 0, P.err, kErrGemmAcc, 64);
     tc_fence_after_sync();
