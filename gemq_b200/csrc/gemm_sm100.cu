@@ -38,6 +38,19 @@ constexpr int kTileBytes = kGemmBN * kGemmBK * 2;  // 16 KB: a B tile, or one 12
 
 enum { kErrGemmAFull = 11, kErrGemmBFull = 12, kErrGemmEmpty = 13, kErrGemmAcc = 14 };
 
+#ifdef GEMQ_GEMM_TRACE
+// Development aid: nanosecond stamps of one CTA's roles (compiled out of the product build).
+__device__ unsigned long long g_gtrace[8][80];
+__device__ __forceinline__ unsigned long long gemm_gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define GTRACE(row, i) do { if (blockIdx.x == 10 && blockIdx.y == 2 && (i) < 80) g_gtrace[row][i] = gemm_gtime(); } while (0)
+#else
+#define GTRACE(row, i) do { } while (0)
+#endif
+
 struct alignas(64) GemmParams {
   CUtensorMap a_map;        // activations [rows, K] (16-bit), box 64 x 256, 128B swizzle
   const uint32_t* wq[2];    // stacked packed words ([0] only unless UP)
@@ -217,6 +230,7 @@ __device__ __forceinline__ void produce_loop(GemmSmem& S, const GemmParams& P, i
   auto produce = [&](const WSet& W, int kb) {
     const int s = kb % kGemmStages;
     mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
+    if ((tid & 255) == 0) GTRACE(0, kb);
 #pragma unroll
     for (int m = 0; m < NMAT; ++m) {
       const __half2 s2 = __half2half2(W.sc[m]), z2 = __half2half2(W.zr[m]);
@@ -227,6 +241,7 @@ __device__ __forceinline__ void produce_loop(GemmSmem& S, const GemmParams& P, i
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
     __syncwarp();
     if (lane == 0) mbar_arrive(&S.b_full[s]);
+    if ((tid & 255) == 0) GTRACE(1, kb);
   };
   if (grp < KB) fetch(ring[0], grp);
   if (grp + 2 < KB) fetch(ring[1], grp + 2);
@@ -354,31 +369,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
         mbar_arrive_expect_tx(&S.a_full[s], 2 * kTileBytes);
         tma_load_2d(S.a[s], &P.a_map, kb * kGemmBK, row0, &S.a_full[s]);
+        GTRACE(2, kb);
       }
     }
   } else {
     // ---- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(BF16 ? 1 : 0, kMmaM, kGemmBN);
+      // Gate/up pass: the two B tiles of a stage are adjacent (256 rows of the same swizzled
+      // layout), so one N = 256 instruction per row half covers both and reads A once.
+      const uint32_t idesc = umma_idesc_f16(BF16 ? 1 : 0, kMmaM, NMAT * kGemmBN);
       const int halves = rows > kMmaM ? 2 : 1;
       for (int kb = 0; kb < KB; ++kb) {
         const int s = kb % kGemmStages;
         const uint32_t par = (kb / kGemmStages) & 1;
         mbar_wait(&S.a_full[s], par, P.err, kErrGemmAFull, 32);
+        GTRACE(3, kb);
         mbar_wait(&S.b_full[s], par, P.err, kErrGemmBFull, 32);
+        GTRACE(4, kb);
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(S.a[s]);
 #pragma unroll
         for (int k4 = 0; k4 < kGemmBK / 16; ++k4) {
-#pragma unroll
-          for (int m = 0; m < NMAT; ++m) {
-            const uint64_t bd = umma_desc_k_sw128(smem_u32(S.b[s][m]) + k4 * 32);
-            for (int hf = 0; hf < halves; ++hf)
-              umma_f16(tmem + (hf * NMAT + m) * 128, umma_desc_k_sw128(a_addr + hf * kTileBytes + k4 * 32), bd, idesc,
-                       (kb | k4) != 0);
-          }
+          const uint64_t bd = umma_desc_k_sw128(smem_u32(S.b[s][0]) + k4 * 32);
+          for (int hf = 0; hf < halves; ++hf)
+            umma_f16(tmem + hf * NMAT * 128, umma_desc_k_sw128(a_addr + hf * kTileBytes + k4 * 32), bd, idesc,
+                     (kb | k4) != 0);
         }
         umma_commit(&S.empty[s]);  // stage is free once these MMAs have read it
+        GTRACE(5, kb);
       }
       umma_commit(&S.acc_full);
     }
@@ -745,3 +763,9 @@ extern "C" const int32_t* gemq_moe_prefill_error_word(const gemq_moe_layer_t* L,
   prefill_bytes(L, tokens, &S, static_cast<char*>(scratch));
   return S.err;
 }
+
+#ifdef GEMQ_GEMM_TRACE
+extern "C" int gemq_debug_read_gemm_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, gemq::g_gtrace, sizeof(gemq::g_gtrace)) == cudaSuccess ? 0 : -1;
+}
+#endif
