@@ -191,9 +191,8 @@ __device__ __forceinline__ void dequant32_b3(unsigned char* brow, int swz, int c
 // path of the stage ring.  Everything that does not change along k (bit width, expert offsets,
 // words per window) is fixed outside the loop: the loop body is loads at constant strides, the
 // de-quantisation and one barrier arrival.
-template <bool UP, bool BF16, int B>
+template <int NMAT, bool BF16, int B>
 __device__ __forceinline__ void produce_loop(GemmSmem& S, const GemmParams& P, int expert, int n0, int KB) {
-  constexpr int NMAT = UP ? 2 : 1;
   constexpr int EPS = B == 3 ? 10 : 32 / B;
   constexpr int NW = B == 3 ? 4 : 32 / EPS;  // words that cover a 32-element window (3-bit: 4 for every even start)
   const int tid = threadIdx.x, lane = tid & 31;
@@ -280,13 +279,19 @@ __device__ __forceinline__ void store_act32(void* dst, const float (&v)[32]) {
   for (int i = 0; i < 4; ++i) d[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
-// UP: two weight tensors (gate, up), epilogue silu(x1) * x3.  !UP: one tensor, optional row weight.
-template <bool UP, bool BF16>
+// MODE kGemmUp: two weight tensors (gate, up), 128 columns of each, epilogue silu(x1) * x3.
+// MODE kGemmWide: one tensor, 256 columns per CTA (the second B tile is the same tensor 128
+// columns further: twice the work per activation tile, which is what the L2-to-SM traffic of the
+// activation tiles asks for); MODE kGemmNarrow: one tensor, 128 columns.  Optional row weight.
+enum { kGemmNarrow = 0, kGemmUp = 1, kGemmWide = 2 };
+
+template <int MODE, bool BF16>
 __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmParams P) {
+  constexpr bool UP = MODE == kGemmUp;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   GemmSmem& S = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mt = blockIdx.y, n0 = blockIdx.x * kGemmBN;
+  const int mt = blockIdx.y, n0 = blockIdx.x * kGemmBN * (MODE == kGemmWide ? 2 : 1);
   int expert = 0, row0 = mt * kGemmBM, rows = 0;
   if (P.tile_expert) {
     if (mt >= *P.n_tiles) return;  // uniform: before any barrier or TMEM allocation
@@ -298,8 +303,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     if (rows <= 0) return;
     if (P.single_expert) expert = static_cast<int>(*P.single_expert);
   }
-  constexpr int NMAT = UP ? 2 : 1;
-  constexpr uint32_t TCOLS = UP ? 512 : 256;  // (row half, matrix) accumulators of 128 columns each
+  constexpr int NMAT = MODE == kGemmNarrow ? 1 : 2;
+  constexpr uint32_t TCOLS = NMAT * 256;  // (row half, matrix) accumulators of 128 columns each
   const int KB = P.K / kGemmBK;
 
   if (tid == 0) {
@@ -323,10 +328,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
   if (warp < kGemmProducerWarps) {
     // ---- B producers ---------------------------------------------------------------------------
     const int bits = P.nbits ? P.nbits[expert] : P.fixed_bits;
-    if (bits == 1) produce_loop<UP, BF16, 1>(S, P, expert, n0, KB);
-    else if (bits == 2) produce_loop<UP, BF16, 2>(S, P, expert, n0, KB);
-    else if (bits == 3) produce_loop<UP, BF16, 3>(S, P, expert, n0, KB);
-    else produce_loop<UP, BF16, 4>(S, P, expert, n0, KB);
+    if (bits == 1) produce_loop<NMAT, BF16, 1>(S, P, expert, n0, KB);
+    else if (bits == 2) produce_loop<NMAT, BF16, 2>(S, P, expert, n0, KB);
+    else if (bits == 3) produce_loop<NMAT, BF16, 3>(S, P, expert, n0, KB);
+    else produce_loop<NMAT, BF16, 4>(S, P, expert, n0, KB);
     // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = tile rows -------------------------
     mbar_wait(&S.acc_full, 0, P.err, kErrGemmAcc, 64);
     tc_fence_after_sync();
@@ -358,6 +363,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
           for (int i = 0; i < 32; ++i) v[i] = act_round<BF16>(__uint_as_float(d1[i])) * rw;
         }
         if (row_on) store_act32<BF16>(orow + c0 * 2, v);
+        if (MODE == kGemmWide) {  // the second 128 columns
+          tmem_ld32(tbase + 128 + c0, d1);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = act_round<BF16>(__uint_as_float(d1[i])) * rw;
+          if (row_on) store_act32<BF16>(orow + (kGemmBN + c0) * 2, v);
+        }
       }
     }
     tc_fence_before_sync();
@@ -534,27 +545,33 @@ __global__ void prefill_combine_kernel(const int* __restrict__ inv, const long l
 // ---- host ---------------------------------------------------------------------------------------
 static bool gemm_shape_ok(int N, int K, int G) { return N % kGemmBN == 0 && K % kGemmBK == 0 && G % kGemmBK == 0 && K % G == 0; }
 
-template <bool UP, bool BF16>
+template <int MODE, bool BF16>
 static int launch_gemm_t(GemmParams& P, int n_mtiles_bound, cudaStream_t stream) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   const size_t smem = sizeof(GemmSmem) + 1024;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(grouped_gemm_kernel<UP, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return GEMQ_ERR_LAUNCH;
     attr_set[dev] = true;
   }
   if (n_mtiles_bound <= 0 || n_mtiles_bound > 65535) return GEMQ_ERR_BAD_SHAPE;
-  const dim3 grid(P.N / kGemmBN, n_mtiles_bound);
-  grouped_gemm_kernel<UP, BF16><<<grid, kGemmThreads, smem, stream>>>(P);
+  const dim3 grid(P.N / (MODE == kGemmWide ? 2 * kGemmBN : kGemmBN), n_mtiles_bound);
+  grouped_gemm_kernel<MODE, BF16><<<grid, kGemmThreads, smem, stream>>>(P);
   return launch_status();
 }
 
 int launch_gemm(GemmParams& P, bool up, bool bf16, int n_mtiles_bound, cudaStream_t stream) {
-  if (up) return bf16 ? launch_gemm_t<true, true>(P, n_mtiles_bound, stream) : launch_gemm_t<true, false>(P, n_mtiles_bound, stream);
-  return bf16 ? launch_gemm_t<false, true>(P, n_mtiles_bound, stream) : launch_gemm_t<false, false>(P, n_mtiles_bound, stream);
+  if (up) return bf16 ? launch_gemm_t<kGemmUp, true>(P, n_mtiles_bound, stream) : launch_gemm_t<kGemmUp, false>(P, n_mtiles_bound, stream);
+  if (P.N % (2 * kGemmBN) == 0) {  // 256 columns per CTA: the second B tile is the same tensor, 128 columns on
+    P.wq[1] = P.wq[0] + kGemmBN;
+    P.scales[1] = P.scales[0] + kGemmBN;
+    P.zeros[1] = P.zeros[0] + kGemmBN;
+    return bf16 ? launch_gemm_t<kGemmWide, true>(P, n_mtiles_bound, stream) : launch_gemm_t<kGemmWide, false>(P, n_mtiles_bound, stream);
+  }
+  return bf16 ? launch_gemm_t<kGemmNarrow, true>(P, n_mtiles_bound, stream) : launch_gemm_t<kGemmNarrow, false>(P, n_mtiles_bound, stream);
 }
 
 }  // namespace gemq
