@@ -87,6 +87,7 @@ struct JobInfo {
 
 struct Range {
   int job, ulo, uhi;
+  int rev;  // walk the range from its last chunk to its first
 };
 
 struct StreamSmem {
@@ -99,7 +100,6 @@ struct StreamSmem {
   JobInfo info[kMaxJobs];
   Range ranges[kMaxJobs];
   int n_ranges;
-  int pair_mode;  // gate/up launches: the units of jobs (2i, 2i+1) interleave chunk by chunk
 };
 
 struct Unit {
@@ -133,36 +133,38 @@ __device__ __forceinline__ void make_unit(const GemvJob& J, const JobInfo& I, in
   U.nrows = I.bits == 3 ? min(kUnitRows, I.kw - U.wr0) : U.ng * (4 * I.bits);
 }
 
-// Walks this CTA's parts in order; identical in every role.
+// Walks this CTA's parts in order; identical in every role.  The ranges of odd jobs of a fused
+// launch are walked backwards: the chunks of a finish group (gate and up member, or the experts
+// of a combine) are then completed about as often by the even job's CTA as by the odd job's, and
+// with them the draining of the partial slots, which otherwise piles up on the odd jobs' CTAs.
 struct PartWalk {
   int r, u;
+  __device__ __forceinline__ static int first(const Range& R) { return R.rev ? R.uhi : R.ulo; }
   __device__ __forceinline__ void begin(const StreamSmem& S) {
     r = 0;
-    u = S.n_ranges > 0 ? S.ranges[0].ulo : 0;
+    u = S.n_ranges > 0 ? first(S.ranges[0]) : 0;
   }
   __device__ __forceinline__ bool next(const StreamSmem& S, Part& Pt) {
-    while (r < S.n_ranges && u >= S.ranges[r].uhi) {
+    while (r < S.n_ranges && (S.ranges[r].rev ? u <= S.ranges[r].ulo : u >= S.ranges[r].uhi)) {
       ++r;
-      if (r < S.n_ranges) u = S.ranges[r].ulo;
+      if (r < S.n_ranges) u = first(S.ranges[r]);
     }
     if (r >= S.n_ranges) return false;
     const Range& R = S.ranges[r];
     const int sl = S.info[R.job].slices;
-    if (S.pair_mode) {
-      // unit order of a pair: chunk, then member (gate, up), then slice: a CTA that owns a whole
-      // chunk of both members finishes it without touching global memory
-      Pt.chunk = u / (2 * sl);
-      const int rem = u - Pt.chunk * 2 * sl;
-      const int m = rem >= sl ? 1 : 0;
-      Pt.job = R.job + m;
-      Pt.sa = rem - m * sl;
+    Pt.job = R.job;
+    if (R.rev) {
+      Pt.chunk = (u - 1) / sl;
+      const int lo = max(R.ulo, Pt.chunk * sl);
+      Pt.sa = lo - Pt.chunk * sl;
+      Pt.sb = u - Pt.chunk * sl;
+      u = lo;
     } else {
-      Pt.job = R.job;
       Pt.chunk = u / sl;
       Pt.sa = u - Pt.chunk * sl;
+      Pt.sb = min(sl, Pt.sa + (R.uhi - u));
+      u += Pt.sb - Pt.sa;
     }
-    Pt.sb = min(sl, Pt.sa + (R.uhi - u));
-    u += Pt.sb - Pt.sa;
     return true;
   }
 };
@@ -211,15 +213,6 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P, const PlanArgs& J)
     unit_cost = max(1u, chunk_cost / I.slices);
     n_units = static_cast<unsigned>(I.nch) * I.slices;
   }
-  // Gate/up launches: members of a pair have the same shape and bit width (they share the
-  // expert); then the even lane ranges over both members' units.
-  bool pair = false;
-  if (P.epi == kEpiUpPair) {
-    const unsigned other = __shfl_xor_sync(0xffffffffu, n_units, 1), other_cost = __shfl_xor_sync(0xffffffffu, unit_cost, 1);
-    pair = __all_sync(0xffffffffu, lane >= P.n_jobs || (other == n_units && other_cost == unit_cost));
-    if (pair) n_units = (lane & 1) ? 0u : 2u * n_units;
-  }
-  if (lane == 0) S.pair_mode = pair ? 1 : 0;
   const unsigned w = n_units * unit_cost;
   unsigned incl = w;
 #pragma unroll
@@ -246,6 +239,7 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P, const PlanArgs& J)
   if (have) {
     Range R;
     R.job = lane; R.ulo = static_cast<int>(ulo); R.uhi = static_cast<int>(uhi);
+    R.rev = (P.epi != kEpiStore) && (lane & 1);
     S.ranges[__popc(ballot & ((1u << lane) - 1u))] = R;
   }
   if (lane == 0) S.n_ranges = __popc(ballot);
@@ -797,16 +791,6 @@ __device__ __forceinline__ float4 round_half4(const float4& v) {
                      __half2float(__float2half_rn(v.z)), __half2float(__float2half_rn(v.w)));
 }
 
-// Gate/up pair: x1 and x3 rounded to fp16 as the reference stores them, h = silu(x1) * x3 in fp32.
-__device__ __forceinline__ void write_up_pair(const GemvJob& J1, const GemvJob& J3, int n, const float4& s1, const float4& s3) {
-  const float4 a = round_half4(s1), b = round_half4(s3);
-  if (J1.y) store_half4(J1.y + n, a);
-  if (J3.y) store_half4(J3.y + n, b);
-  if (J1.h)
-    *reinterpret_cast<float4*>(J1.h + n) =
-        make_float4(silu_f32(a.x) * b.x, silu_f32(a.y) * b.y, silu_f32(a.z) * b.z, silu_f32(a.w) * b.w);
-}
-
 __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Part& Pt, int n) {
   if (P.epi == kEpiStore) {
     const GemvJob& J = P.jobs[Pt.job];
@@ -815,8 +799,13 @@ __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Par
     const int j1 = Pt.job & ~1, j3 = j1 + 1;
     const GemvJob& J1 = P.jobs[j1];
     const GemvJob& J3 = P.jobs[j3];
-    write_up_pair(J1, J3, n, drain_slots(P, J1, S.info[j1].slices, Pt.chunk, n),
-                  drain_slots(P, J3, S.info[j3].slices, Pt.chunk, n));
+    const float4 a = round_half4(drain_slots(P, J1, S.info[j1].slices, Pt.chunk, n));
+    const float4 b = round_half4(drain_slots(P, J3, S.info[j3].slices, Pt.chunk, n));
+    if (J1.y) store_half4(J1.y + n, a);
+    if (J3.y) store_half4(J3.y + n, b);
+    if (J1.h)
+      *reinterpret_cast<float4*>(J1.h + n) =
+          make_float4(silu_f32(a.x) * b.x, silu_f32(a.y) * b.y, silu_f32(a.z) * b.z, silu_f32(a.w) * b.w);
   } else {
     float4 accw = make_float4(0.f, 0.f, 0.f, 0.f), res = accw;
     for (int i = 0; i < P.n_jobs; ++i) {
@@ -836,58 +825,11 @@ __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Par
   }
 }
 
-// A part's sums (columns 4*lane .. 4*lane+3 of its chunk) that could not be finished on chip:
-// they go to the part's partial slot; the warp that completes the chunk's finish group adds the
-// slots in order and runs the epilogue.
-__device__ __noinline__ void submit_part(const StreamSmem& S, const GemvParams& P, int job, int chunk, int sa, int sb,
-                                         float4 r) {
-  Part Pt;
-  Pt.job = job; Pt.chunk = chunk; Pt.sa = sa; Pt.sb = sb;
-  const int lane = threadIdx.x & 31;
-  const GemvJob& J = P.jobs[Pt.job];
-  const JobInfo& I = S.info[Pt.job];
-  const int n = Pt.chunk * 128 + 4 * lane;
-  const bool col_on = n < J.N;
-  if (col_on) __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(Pt.sa) * P.c_total + J.col_base + n), r);
-  if (lane == 0) atomicOr(reinterpret_cast<unsigned*>(P.counters + J.mask_base + Pt.chunk), 1u << (Pt.sa & 31));
-  __threadfence();
-  __syncwarp();
-  int last = 0;
-  if (lane == 0) {
-    int expected = I.slices;
-    int* ctr = P.counters + J.chunk_base + Pt.chunk;
-    if (P.epi == kEpiUpPair) expected = S.info[Pt.job & ~1].slices + S.info[(Pt.job & ~1) + 1].slices;
-    if (P.epi == kEpiCombine) {
-      expected = 0;
-      for (int i = 0; i < P.n_jobs; ++i) expected += S.info[i].slices;
-    }
-    const int add = Pt.sb - Pt.sa;
-    const int old = atomicAdd(ctr, add);
-    last = (old + add == expected);
-    if (last) *ctr = 0;
-  }
-  last = __shfl_sync(0xffffffffu, last, 0);
-  if (last) {
-    __threadfence();
-    if (col_on) finish_group(S, P, Pt, n);
-    __syncwarp();
-    if (lane == 0) {  // every lane has read the slot sets of the jobs it drained: clear them
-      const int j0 = P.epi == kEpiStore ? Pt.job : (P.epi == kEpiUpPair ? (Pt.job & ~1) : 0);
-      const int j1 = P.epi == kEpiStore ? Pt.job + 1 : (P.epi == kEpiUpPair ? j0 + 2 : P.n_jobs);
-      for (int j = j0; j < j1; ++j) P.counters[P.jobs[j].mask_base + Pt.chunk] = 0;
-    }
-  }
-}
-
 __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
   const int lane = threadIdx.x & 31;
   PartWalk W;
   W.begin(S);
   Part Pt;
-  // gate/up launches: a whole gate chunk waits here for the up chunk that usually follows it
-  int held_job = 0, held_chunk = 0, held_sb = 0;
-  float4 held_r = make_float4(0.f, 0.f, 0.f, 0.f);
-  bool holding = false;
   for (int pc = 0; W.next(S, Pt); ++pc) {
     const GemvJob& J = P.jobs[Pt.job];
     const JobInfo& I = S.info[Pt.job];
@@ -903,34 +845,45 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
     __syncwarp();
     if (lane == 0) mbar_arrive(&S.redempty[slot]);
 
-    const int n = Pt.chunk * 128 + 4 * lane;
-    const bool col_on = n < J.N;
+    const int n0 = Pt.chunk * 128;
+    const int ncols = min(128, J.N - n0);
+    const bool col_on = 4 * lane < ncols;
+    const int n = n0 + 4 * lane;
     const bool whole = Pt.sa == 0 && Pt.sb == I.slices;
     if (whole && P.epi == kEpiStore) {
       if (col_on) store_half4(J.y + n, r);
       continue;
     }
-    if (P.epi == kEpiUpPair && whole) {
-      if (!(Pt.job & 1)) {  // gate member: hold it
-        if (holding) submit_part(S, P, held_job, held_chunk, 0, held_sb, held_r);
-        held_job = Pt.job; held_chunk = Pt.chunk; held_sb = Pt.sb;
-        held_r = r;
-        holding = true;
-        continue;
+    if (col_on) __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(Pt.sa) * P.c_total + J.col_base + n), r);
+    if (lane == 0) atomicOr(reinterpret_cast<unsigned*>(P.counters + J.mask_base + Pt.chunk), 1u << (Pt.sa & 31));
+    __threadfence();
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      int expected = I.slices;
+      int* ctr = P.counters + J.chunk_base + Pt.chunk;
+      if (P.epi == kEpiUpPair) expected = S.info[Pt.job & ~1].slices + S.info[(Pt.job & ~1) + 1].slices;
+      if (P.epi == kEpiCombine) {
+        expected = 0;
+        for (int i = 0; i < P.n_jobs; ++i) expected += S.info[i].slices;
       }
-      if (holding && held_job == Pt.job - 1 && held_chunk == Pt.chunk) {  // the pair is complete on chip
-        if (col_on) write_up_pair(P.jobs[held_job], J, n, held_r, r);
-        holding = false;
-        continue;
+      const int add = Pt.sb - Pt.sa;
+      const int old = atomicAdd(ctr, add);
+      last = (old + add == expected);
+      if (last) *ctr = 0;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      __threadfence();
+      if (col_on) finish_group(S, P, Pt, n);
+      __syncwarp();
+      if (lane == 0) {  // every lane has read the slot sets of the jobs it drained: clear them
+        const int j0 = P.epi == kEpiStore ? Pt.job : (P.epi == kEpiUpPair ? (Pt.job & ~1) : 0);
+        const int j1 = P.epi == kEpiStore ? Pt.job + 1 : (P.epi == kEpiUpPair ? j0 + 2 : P.n_jobs);
+        for (int j = j0; j < j1; ++j) P.counters[P.jobs[j].mask_base + Pt.chunk] = 0;
       }
     }
-    if (holding) {
-      submit_part(S, P, held_job, held_chunk, 0, held_sb, held_r);
-      holding = false;
-    }
-    submit_part(S, P, Pt.job, Pt.chunk, Pt.sa, Pt.sb, r);
   }
-  if (holding) submit_part(S, P, held_job, held_chunk, 0, held_sb, held_r);
 }
 
 __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_constant__ GemvParams P) {
