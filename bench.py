@@ -251,6 +251,9 @@ def run_prefill(args, rank, local_rank, world):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "mixtral8x7b_moe_layer_prefill_4096tok_top2_dirichlet0.5_mixed_bits (config 3)",
                        "bits": bits, "tokens_per_rank": hi - lo, "parallelism": f"expert-parallel x{world}",
+                       # share of the routed rows that lands on the busiest rank (1/world = perfectly even)
+                       "busiest_rank_row_share": float(torch.bincount(sel_all.view(-1) // max(1, E // world),
+                                                                      minlength=world).max()) / sel_all.numel(),
                        "l2": "inputs larger than L2: ~0.4 GB of packed weights per step"},
             "e2e": {"value": T * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * D // world,
                     "d2h_bytes_per_step": 2 * T * D // world},
