@@ -735,12 +735,12 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
 // A word per (job, chunk) records which slots hold a partial (one bit per part, at the part's
 // first slice): only those are read, a few at a time so that their latencies overlap.  Jobs
 // with more than 32 slices scan every slot.
-__device__ __noinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J, int slices, int chunk, int n) {
+// (Arguments by value: a reference to the kernel parameters would turn every access into a generic load.)
+__device__ __noinline__ float4 drain_slots(float* src, size_t c_total, const unsigned* slot_set, int slices) {
   constexpr int kBatch = 4;
-  float* src = P.partial + J.col_base + n;
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
   if (slices <= 32) {
-    unsigned m = __ldcg(reinterpret_cast<const unsigned*>(P.counters + J.mask_base + chunk));
+    unsigned m = __ldcg(slot_set);
     while (m) {
       float4 t[kBatch];
       float4* q[kBatch];
@@ -750,7 +750,7 @@ __device__ __noinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J
         if (m) {
           const int s = __ffs(m) - 1;
           m &= m - 1;
-          q[i] = reinterpret_cast<float4*>(src + static_cast<size_t>(s) * P.c_total);
+          q[i] = reinterpret_cast<float4*>(src + static_cast<size_t>(s) * c_total);
           t[i] = __ldcg(q[i]);
         }
       }
@@ -767,12 +767,12 @@ __device__ __noinline__ float4 drain_slots(const GemvParams& P, const GemvJob& J
     float4 t[kBatch];
 #pragma unroll
     for (int i = 0; i < kBatch; ++i)
-      if (s0 + i < slices) t[i] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(s0 + i) * P.c_total));
+      if (s0 + i < slices) t[i] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(s0 + i) * c_total));
 #pragma unroll
     for (int i = 0; i < kBatch; ++i)
       if (s0 + i < slices) {
         sum.x += t[i].x; sum.y += t[i].y; sum.z += t[i].z; sum.w += t[i].w;
-        __stcg(reinterpret_cast<float4*>(src + static_cast<size_t>(s0 + i) * P.c_total), make_float4(0.f, 0.f, 0.f, 0.f));
+        __stcg(reinterpret_cast<float4*>(src + static_cast<size_t>(s0 + i) * c_total), make_float4(0.f, 0.f, 0.f, 0.f));
       }
   }
   return sum;
@@ -794,13 +794,13 @@ __device__ __forceinline__ float4 round_half4(const float4& v) {
 __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Part& Pt, int n) {
   if (P.epi == kEpiStore) {
     const GemvJob& J = P.jobs[Pt.job];
-    store_half4(J.y + n, drain_slots(P, J, S.info[Pt.job].slices, Pt.chunk, n));
+    store_half4(J.y + n, drain_slots(P.partial + J.col_base + n, P.c_total, reinterpret_cast<const unsigned*>(P.counters + J.mask_base + Pt.chunk), S.info[Pt.job].slices));
   } else if (P.epi == kEpiUpPair) {
     const int j1 = Pt.job & ~1, j3 = j1 + 1;
     const GemvJob& J1 = P.jobs[j1];
     const GemvJob& J3 = P.jobs[j3];
-    const float4 a = round_half4(drain_slots(P, J1, S.info[j1].slices, Pt.chunk, n));
-    const float4 b = round_half4(drain_slots(P, J3, S.info[j3].slices, Pt.chunk, n));
+    const float4 a = round_half4(drain_slots(P.partial + J1.col_base + n, P.c_total, reinterpret_cast<const unsigned*>(P.counters + J1.mask_base + Pt.chunk), S.info[j1].slices));
+    const float4 b = round_half4(drain_slots(P.partial + J3.col_base + n, P.c_total, reinterpret_cast<const unsigned*>(P.counters + J3.mask_base + Pt.chunk), S.info[j3].slices));
     if (J1.y) store_half4(J1.y + n, a);
     if (J3.y) store_half4(J3.y + n, b);
     if (J1.h)
@@ -810,7 +810,7 @@ __device__ void finish_group(const StreamSmem& S, const GemvParams& P, const Par
     float4 accw = make_float4(0.f, 0.f, 0.f, 0.f), res = accw;
     for (int i = 0; i < P.n_jobs; ++i) {
       const GemvJob& Ji = P.jobs[i];
-      const float4 x2 = round_half4(drain_slots(P, Ji, S.info[i].slices, Pt.chunk, n));
+      const float4 x2 = round_half4(drain_slots(P.partial + Ji.col_base + n, P.c_total, reinterpret_cast<const unsigned*>(P.counters + Ji.mask_base + Pt.chunk), S.info[i].slices));
       if (Ji.y) store_half4(Ji.y + n, x2);
       if (i < P.comb_weighted) {
         const float wgt = __half2float(P.comb_w[i]);

@@ -125,15 +125,32 @@ def test_gemm_tc_vs_oracle():
     """tcgen05 GEMM: single matrix, every bit-width, ragged last row tile."""
     from gemq_b200.kernels import dequant_gemm
     from gemq_b200.kernels._runtime import error_word
+    for N in (256, 384):  # 256 columns per CTA, and the 128-column form (N not a multiple of 256)
+        for b in (1, 2, 3, 4):
+            rng = np.random.default_rng(40 + b + N)
+            K, M = 512, 200
+            lin = MF.draw_linear(rng, N, K, b)
+            x = rng.standard_normal((M, K)).astype(np.float16)
+            t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+            y = dequant_gemm(t(x), t(lin["wq"]), t(lin["s"]), t(lin["z"]), b, 128)
+            assert int(error_word(y.device).item()) == 0
+            check(y, O.dequant_gemm(x, lin["wq"], lin["s"], lin["z"], b, 128))
+
+
+def test_gemm_tc_weights_bit_exact():
+    """Identity activations read the de-quantised weights back through the tensor cores:
+    they must equal the reference's fp16(fma(q, s, z)) bit for bit, at every bit width
+    (3-bit: all five window offsets inside a word occur within 160 reduction elements)."""
+    from gemq_b200.kernels import dequant_gemm
     for b in (1, 2, 3, 4):
-        rng = np.random.default_rng(40 + b)
-        N, K, M = 256, 512, 200
+        rng = np.random.default_rng(70 + b)
+        N, K = 384, 640
         lin = MF.draw_linear(rng, N, K, b)
-        x = rng.standard_normal((M, K)).astype(np.float16)
+        x = np.eye(K, dtype=np.float16)
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
         y = dequant_gemm(t(x), t(lin["wq"]), t(lin["s"]), t(lin["z"]), b, 128)
-        assert int(error_word(y.device).item()) == 0
-        check(y, O.dequant_gemm(x, lin["wq"], lin["s"], lin["z"], b, 128))
+        want = O.dequantize(lin["wq"], lin["s"], lin["z"], b, 128, K)  # [K, N] fp16
+        assert np.array_equal(y.cpu().numpy().view(np.uint16), np.ascontiguousarray(want).view(np.uint16)), f"bits={b}"
 
 
 def test_mixtral_prefill_grouped_gemm():
