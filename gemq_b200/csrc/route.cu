@@ -32,7 +32,9 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
 //         activation dtype (softmax/topk/renorm of a half tensor);
 // mode 1: logits rounded to the activation dtype, softmax and renormalisation in fp32;
 // mode 2: fp32 throughout.  The returned weights are cast to the activation dtype.
-template <typename T>
+// PER: experts per lane in the softmax / top-k phase (E <= 32 * PER); the small instances keep the
+// serial tail of the kernel (one warp) short.
+template <typename T, int PER>
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restrict__ x, const T* __restrict__ gate,
                                                               int D, int E, int A, int mode, int renorm,
                                                               long long* __restrict__ idx, T* __restrict__ weights,
@@ -92,7 +94,6 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restric
   __syncthreads();
   if (warp != 0) return;
 
-  constexpr int PER = kRouteMaxExperts / 32;
   float p[PER];
   float mx = -INFINITY;
 #pragma unroll
@@ -117,9 +118,9 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restric
     if (mode == 0) p[i] = Act<T>::to_f(Act<T>::from_f(p[i]));
     if ((lane + 32 * i) >= E) p[i] = -1.f;
   }
-  // top-k: A rounds of warp arg-max, ties to the lower expert id
-  float wsel[kRouteMaxTopK];
-  int isel[kRouteMaxTopK];
+  // top-k: A rounds of warp arg-max, ties to the lower expert id; lane a keeps the a-th winner
+  float my_w = 0.f;
+  int my_i = 0;
   for (int a = 0; a < A; ++a) {
     float bv = -2.f;
     int bi = 0x7fffffff;
@@ -132,22 +133,18 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const T* __restric
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
-    wsel[a] = bv;
-    isel[a] = bi;
+    if (lane == a) { my_w = bv; my_i = bi; }
 #pragma unroll
     for (int i = 0; i < PER; ++i)
       if (lane + 32 * i == bi) p[i] = -3.f;
   }
-  if (lane == 0) {
-    float tot = 0.f;
-    for (int a = 0; a < A; ++a) tot += wsel[a];
-    if (mode == 0) tot = Act<T>::to_f(Act<T>::from_f(tot));
-    for (int a = 0; a < A; ++a) {
-      float w = wsel[a];
-      if (renorm) w = w / tot;
-      idx[static_cast<size_t>(t) * A + a] = isel[a];
-      weights[static_cast<size_t>(t) * A + a] = Act<T>::from_f(w);
-    }
+  float tot = 0.f;
+  for (int a = 0; a < A; ++a) tot += __shfl_sync(0xffffffffu, my_w, a);  // in selection order, like a sum over the top-k tensor
+  if (mode == 0) tot = Act<T>::to_f(Act<T>::from_f(tot));
+  if (lane < A) {
+    const float w = renorm ? my_w / tot : my_w;
+    idx[static_cast<size_t>(t) * A + lane] = my_i;
+    weights[static_cast<size_t>(t) * A + lane] = Act<T>::from_f(w);
   }
 }
 
@@ -171,14 +168,17 @@ extern "C" int gemq_moe_route(const void* x, const void* gate, int tokens, int D
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e;
-  if (x_is_bf16)
-    e = cudaLaunchKernelEx(&cfg, route_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x),
-                           static_cast<const __nv_bfloat16*>(gate), D, E, A, mode, renorm,
-                           reinterpret_cast<long long*>(idx), static_cast<__nv_bfloat16*>(weights), logits);
-  else
-    e = cudaLaunchKernelEx(&cfg, route_kernel<__half>, static_cast<const __half*>(x),
-                           static_cast<const __half*>(gate), D, E, A, mode, renorm,
-                           reinterpret_cast<long long*>(idx), static_cast<__half*>(weights), logits);
+  auto launch = [&](auto kernel_h, auto kernel_b) {
+    return x_is_bf16 ? cudaLaunchKernelEx(&cfg, kernel_b, static_cast<const __nv_bfloat16*>(x),
+                                          static_cast<const __nv_bfloat16*>(gate), D, E, A, mode, renorm,
+                                          reinterpret_cast<long long*>(idx), static_cast<__nv_bfloat16*>(weights), logits)
+                     : cudaLaunchKernelEx(&cfg, kernel_h, static_cast<const __half*>(x), static_cast<const __half*>(gate), D,
+                                          E, A, mode, renorm, reinterpret_cast<long long*>(idx),
+                                          static_cast<__half*>(weights), logits);
+  };
+  if (E <= 32) e = launch(route_kernel<__half, 1>, route_kernel<__nv_bfloat16, 1>);
+  else if (E <= 64) e = launch(route_kernel<__half, 2>, route_kernel<__nv_bfloat16, 2>);
+  else e = launch(route_kernel<__half, kRouteMaxExperts / 32>, route_kernel<__nv_bfloat16, kRouteMaxExperts / 32>);
   if (e != cudaSuccess) return GEMQ_ERR_LAUNCH;
   return launch_status();
 }
