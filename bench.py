@@ -260,7 +260,9 @@ def run_prefill(args, rank, local_rank, world):
             "gpu_launches": 7 * args.steps, "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (gate/up + down; whole prefill call timed)",
                          "achieved": ach / world, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / world / peak_tf,
-                         "traffic": None}}))
+                         # ncu (profiles/grouped_gemm_kernel_prefill_4096_tokens.md): dram read + write of one
+                         # gate/up launch plus one down launch at N=1, bytes per prefill call
+                         "traffic": (489.2e6 + 220.7e6 + 465.9e6 + 58.8e6) if world == 1 else None}}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
