@@ -16,7 +16,9 @@ import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
 sys.dont_write_bytecode = True
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py <path to a GEMQ checkout>")
+ref_root = sys.argv[1]
 sys.path.insert(0, ref_root)
 
 import numpy as np  # noqa: E402
