@@ -1,26 +1,26 @@
-// Persistent, bulk-copy fed dequant GEMV for one activation row (decode batch 1).
+// Persistent, TMA fed dequant GEMV for one activation row (decode batch 1).
 //
 // One CTA per SM.  The launch's work is cut into units of 64 packed word rows x 128
 // output columns of one job (32 KB of codes plus the group metadata: 2048 / 1024 / 640 /
 // 512 reduction elements at 1 / 2 / 3 / 4 bits).  Units are ordered job-major, column
 // chunk-major, k-slice-minor and dealt to the CTAs in contiguous, byte-balanced ranges, so
-// a CTA usually owns all slices of a chunk and keeps the running sums on chip.  Inside a
-// CTA four roles run concurrently:
+// a CTA usually owns several slices of a chunk and keeps their running sum in registers.
+// Inside a CTA four roles run concurrently:
 //   * a producer warp streams the units into a 4-stage shared-memory ring with tiled TMA
 //     (cp.async.bulk.tensor.2d on the [word rows, N] tensors as they are: four 128B-swizzled
 //     boxes of 64 rows x 32 columns plus 4-row boxes of scales and offsets per unit,
-//     completion through mbarrier transaction counts): about 130 KB per SM are in flight
-//     whatever the other warps are doing;
-//   * a table warp turns the activation slice of each unit into the pre-scaled fp16
-//     operand table of that stage (one power-of-two scale and one sum per group);
-//   * sixteen consumer warps (4 column strips x 4 row quarters) run the in-place
-//     subnormal-fp16 mma.sync scheme described in gemv.cu on the staged words and
-//     accumulate over the consecutive slices of a chunk in registers;
-//   * a finisher warp adds the four row quarters in a fixed order and writes the result:
-//     directly when this CTA covered the whole reduction, otherwise through zero-restoring
-//     fp32 partial slots and an arrival counter (the warp that completes a chunk adds the
-//     slots in order and runs the epilogue).  Global-memory latency of this protocol never
-//     stalls the consumers.
+//     completion through mbarrier transaction counts);
+//   * two table warps (alternate units) turn the activation slice of each unit into the
+//     operand table of that unit, in a six-slot ring of its own: signed base-256 digit planes
+//     for the integer MMA of the 1/2/4-bit units, pre-scaled fp16 values for the 3-bit ones;
+//   * sixteen consumer warps in two groups that take alternate units (4 column strips x 2 row
+//     halves each) feed the packed words, masked in place, to mma.sync as the A operand and
+//     accumulate over the consecutive slices of a part in registers;
+//   * a finisher warp adds the four row parts in a fixed order and writes the result:
+//     directly when this CTA covered the whole reduction of a plain GEMV, otherwise through
+//     zero-restoring fp32 partial slots, a per-chunk set of slots in use and an arrival counter
+//     (the warp that completes a finish group adds the slots in order and runs the epilogue).
+//     Global-memory latency of this protocol never stalls the consumers.
 // Every wait is bounded: on expiry the kernel records an error code and keeps going.
 #include "gemv.cuh"
 #include "ptx.cuh"
