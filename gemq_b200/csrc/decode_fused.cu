@@ -1,0 +1,1443 @@
+// One-token forward of a quantised MoE layer in ONE persistent launch (one CTA per SM):
+// router, fused gate/up projections, SiLU*mul, down projections and the weighted top-k combine
+// (+ shared experts), gemq/inference/moe_block.py:200-235 and :488-531.
+//
+// Work.  Every matrix is cut into quanta of 4 quantisation groups (5 for 3-bit: 640 reduction
+// elements = 64 whole packed rows) times 128 output columns.  Phase 0 lists the quanta of the
+// gate and up projections of the selected experts (slot-major, column chunk, gate|up, k), phase 1
+// those of the down projections; each phase is dealt to the CTAs in contiguous byte-balanced
+// ranges, so the launch streams every selected weight exactly once and all SMs end together.
+// A maximal run of quanta of one (matrix, column chunk) inside a range is a "part".
+//
+// Inside a CTA twelve consumer warps split the reduction dimension of a part (run lanes); each
+// streams its own packed rows straight from global memory through a private ring of
+// asynchronous copies (cp.async).  A task is 4 packed rows x 128 columns: four 512-byte row
+// segments, each fetched by one warp instruction -- the access pattern that reaches the copy
+// bandwidth of the part (128-byte pieces per row stay at half of it); five tasks = 10 KB in
+// flight per warp.  The copies land in shared memory with a 16-byte swizzle so that the
+// MMA-shaped reads (lane = 4 columns of one row) are conflict free.  The scales and offsets of a
+// run travel through the same ring behind its packed rows.  The codes are never de-quantised:
+//   1/2/4-bit: `word & mask` leaves four codes, one per byte, each shifted by its position in the
+//     byte: a ready u8 A operand of mma.sync.m16n8k32.s32.u8.s8.  The B operand is the
+//     activation, per group scaled to 21 bits and split into three balanced base-256 digit planes;
+//     it is loaded once per task and used for all eight 16-column tiles.  Two consecutive groups
+//     ride in MMA columns 0..2 and 4..6 and are folded into the fp32 result with their scales and
+//     offsets every two groups.
+//   3-bit: ten codes per word; `word & mask` leaves two codes in the mantissas of an fp16x2
+//     register (subnormals), the A operand of mma.sync.m16n8k16; five groups ride in columns 0..4.
+// The activation tables (digit planes of x for a bit width, of h = silu(x1)*x3 for a slot) are
+// built once per CTA and kept in shared memory.
+// Four finisher warps (parts round robin) add the twelve run lanes of a part and run the
+// cross-CTA protocol: fp32 partial slots that are restored to zero and one 64-bit word per column
+// chunk that carries the arrival count and the set of slots in use, so that the CTA whose
+// atomic completes a chunk knows which slots to add (in slice order: bit-reproducible) and
+// applies the epilogue (h = silu(x1)*x3 in fp32, or the weighted combine).  An h chunk is a
+// reduction group of the down projections: a flag per chunk lets a CTA build its phase-1 table
+// group by group while the last gate/up chunks are still being finished, and the weight copies of
+// phase 1 are in flight long before.  Every wait is bounded and records an error code.
+#include "gemv.cuh"
+#include "ptx.cuh"
+
+namespace gemq {
+namespace fused {
+
+constexpr int kLanes = 12;                // run lanes of a part: the reduction dimension is dealt to them round robin
+constexpr int kCons = kLanes;             // consumer warps, one per run lane (three per SM sub-partition)
+constexpr int kFin = 4;                   // finisher warps, one per reduction slot
+constexpr int kWarps = kCons + kFin;
+constexpr int kThreads = 32 * kWarps;
+constexpr int kConsThreads = 32 * kCons;
+constexpr int kRing = 6;                  // ring slots per consumer warp (five tasks in flight)
+constexpr int kSlotBytes = 2048;          // a task: 4 packed rows x 128 columns, or the scales | offsets of four groups
+constexpr int kRedSlots = kFin;
+constexpr int kMaxS = kMaxSlots + 1;      // routed slots + merged shared expert
+constexpr int kMaxK = 14336;
+constexpr int kMaxGroups = kMaxK / kGroup;
+constexpr int kMaxParts = 40;
+constexpr int kRouteMaxE = 32;
+constexpr int kMetaE = 64;
+constexpr int kErrSlot = kMaxCounters - 1;   // same word as the other decode kernels
+constexpr int kExitSlot = kMaxCounters - 3;  // CTAs that left this launch
+// words of activation tables: three digit planes of kMaxK bytes (+ padding), or the 3-bit
+// tables (16 halves per packed row + 16 per group for the rows that straddle two groups)
+constexpr int kTabWordsI8 = 3 * (kMaxK / 4 + 16);
+constexpr int kTabWordsB3 = ((kMaxK + 9) / 10) * 8 + 8 + kMaxGroups * 8;
+constexpr int kTabWords = kTabWordsI8 > kTabWordsB3 ? kTabWordsI8 : kTabWordsB3;
+
+enum { kErrRedFull = 11, kErrRedEmpty = 12, kErrPhase = 13 };
+
+
+struct Mat3 {
+  const uint32_t* wq;
+  const __half* sc;
+  const __half* zr;
+};
+
+struct FusedParams {
+  const __half* x;       // [D]
+  const __half* gate;    // [E, D]
+  __half* out;           // [D]
+  long long* idx;        // [A]
+  __half* w;             // [A]
+  int D, F, E, A, SF, S;
+  int do_route, route_mode, renorm;
+  Mat3 w1, w3, w2;       // stacked experts
+  const int* nbits1; const int* wqs1; const int* zss1; const int* zss3;
+  const int* nbits2; const int* wqs2; const int* zss2;
+  Mat3 s1, s3, s2;       // merged shared expert (SF > 0)
+  int sbits;
+  float* partial;        // [slices][c_total], zero between launches
+  int* counters;         // zero between launches
+  float* h;              // [A*F + SF]
+  int c_total;
+};
+
+struct SlotInfo {
+  const uint32_t* wq[3];  // gate, up, down matrix of the slot's expert (row 0)
+  const __half* sc[3];
+  const __half* zr[3];
+  int bits[2];            // gate/up, down
+  int F;                  // gate/up columns = down reduction length
+  int hoff;               // first h element of the slot
+  int nq[2], nch[2];      // quanta per (matrix, chunk); column chunks, per phase
+  int colb[2];            // first partial column of the slot, per phase
+  int ctrb;               // phase 0: first pair counter
+  int maskb[2];           // first slot-set word, per phase
+};
+
+struct PartDesc {
+  const uint32_t* w;      // row 0 of the matrix, first column of the chunk
+  const __half* sc;
+  const __half* zr;
+  int N, B, kw, ngroups;
+  int run_lo, run_hi;     // flush runs (2 groups; 5 for 3-bit) of this part
+  int roff;               // run lane that takes run_lo: the runs of all parts go round the lanes in one sequence
+  int ncols;
+  int tab;                // activation table the part needs: bit width (phase 0) or 8 + slot (phase 1)
+  int phase, s, c;
+  int qa, qb;             // quanta [qa, qb) of the chunk
+  int ctr, expected, mask, colp;
+};
+
+struct Tables {
+  float xsum[kMaxGroups];
+  float fin[kMaxGroups];
+  alignas(16) uint32_t tab[kTabWords];
+};
+
+struct Smem {
+  alignas(128) unsigned char ring[kCons][kRing][kSlotBytes];
+  Tables T;
+  alignas(16) float red[kRedSlots][kLanes][128];
+  alignas(8) unsigned long long redfull[kRedSlots], redempty[kRedSlots];
+  SlotInfo slot[kMaxS];
+  PartDesc parts[kMaxParts];
+  int n_parts, n_parts0, expected1, pairs_total, overflow;
+  int sel_e[kMaxS];
+  __half sel_w[kMaxS];
+  float logit[kRouteMaxE];
+  float part_sum[kRouteMaxE][8];
+  int emeta[7][kMetaE];  // nbits / stride tables of the experts, fetched ahead of the dependency wait
+};
+
+static_assert(sizeof(Smem) <= 227 * 1024 - 64, "shared memory of the layer kernel exceeds the per-CTA limit");
+
+// ---- small helpers ----------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory"); }
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ int clamp_bits(int b) { return b < 1 ? 1 : (b > 4 ? 4 : b); }
+__device__ __forceinline__ int quantum_groups(int bits) { return bits == 3 ? 5 : 4; }
+// relative cost of a quantum, for the byte/issue balanced deal of the quanta to the CTAs
+// (relative time of a quantum measured in place: the low bit widths are bound by the MMA and
+// logic issue rate, not by their bytes)
+__device__ __forceinline__ unsigned quantum_cost(int bits) {
+  return bits == 1 ? 32u : (bits == 2 ? 36u : (bits == 3 ? 98u : 49u));
+}
+
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  float f0 = __int_as_float(d[0]), f1 = __int_as_float(d[1]), f2 = __int_as_float(d[2]), f3 = __int_as_float(d[3]);
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(f0), "+f"(f1), "+f"(f2), "+f"(f3)
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  d[0] = __float_as_int(f0); d[1] = __float_as_int(f1); d[2] = __float_as_int(f2); d[3] = __float_as_int(f3);
+}
+
+// ---- integer operand format (1/2/4-bit) ---------------------------------------------------
+template <int B>
+struct I8 {
+  static constexpr int kEps = 32 / B;
+  static constexpr int kCpb = 8 / B;  // codes per byte = operands per word
+  static constexpr int kPad = B == 1 ? 4 : (B == 2 ? 16 : 8);  // words between the planes (bank spread)
+  static constexpr uint32_t kMask = ((1u << B) - 1u) * 0x01010101u;
+  __device__ static __forceinline__ uint32_t operand(uint32_t w, int q) { return w & (kMask << (B * q)); }
+  __device__ static __forceinline__ int plane_stride(int K) { return K / 4 + kPad; }
+};
+
+// c = 20 - floor(log2(max|x|)): the largest scaled value of a group lands in [2^20, 2^21).
+__device__ __forceinline__ int scale_exp_i8(float mx) {
+  int c = 20 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
+  return c < -60 ? -60 : (c > 60 ? 60 : c);
+}
+// c = 14 - floor(log2(max|x|)) (3-bit: fp16 operands).
+__device__ __forceinline__ int scale_exp_b3(float mx) {
+  int c = 14 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
+  return c < -15 ? -15 : (c > 40 ? 40 : c);
+}
+// round(x * f) + 0x8080 in the low mantissa bits: bytes 0, 1 = low balanced digits + 128, byte 2 = top digit + 64
+__device__ __forceinline__ uint32_t digits_word(float x, float f) { return __float_as_uint(fmaf(x, f, 12615808.0f)); }
+
+// Wait until the h chunks (= reduction groups of phase 1) [g0, g1) of a slot are complete.  Lane 0
+// polls; the flags are written by the finisher that completed the chunk, after a fence.
+__device__ __forceinline__ void wait_groups(const int* flags, int g0, int g1, int* err) {
+  if (flags) {
+    if ((threadIdx.x & 31) == 0) {
+      for (int gq = g0; gq < g1; ++gq) {
+        int i = 0;
+        while (ld_acquire(flags + gq) == 0) {
+          if (++i > kSpinLimit) { atomicExch(err, kErrPhase); break; }
+          __nanosleep(32);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// Digit-plane table of the activation vector for B-bit matrices; the consumer warps take the
+// wanted 32-row blocks round robin.  A group is 4*B consecutive rows (= lanes).
+template <int B>
+__device__ __forceinline__ void build_i8(Tables& T, const void* x, bool xf32, int K, unsigned need, const int* flags,
+                                         int* err, int warp, int lane) {
+  using F = I8<B>;
+  constexpr int EPS = F::kEps, CPB = F::kCpb, LPG = 4 * B;
+  const int rows = K / EPS;
+  const int ps = F::plane_stride(K);
+  int taken = 0;
+  for (int row0 = 0; row0 < rows; row0 += 32) {
+    const int q0 = (row0 / LPG) >> 2, q1 = ((row0 + 31) / LPG) >> 2;
+    if (q0 < 32 && !((need >> q0) & 1u) && !((need >> (q1 < 32 ? q1 : 31)) & 1u)) continue;
+    if ((taken++ % kCons) != warp) continue;
+    wait_groups(flags, row0 / LPG, min(rows, row0 + 32) / LPG, err);
+    const int row = row0 + lane;
+    const bool on = row < rows;
+    float xv[EPS];
+    if (on) {
+      const size_t k = static_cast<size_t>(row) * EPS;
+      if (xf32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + k);
+#pragma unroll
+        for (int i = 0; i < EPS / 4; ++i) {
+          const float4 t = __ldcg(p + i);
+          xv[4 * i] = t.x; xv[4 * i + 1] = t.y; xv[4 * i + 2] = t.z; xv[4 * i + 3] = t.w;
+        }
+      } else {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(x) + k);
+#pragma unroll
+        for (int i = 0; i < EPS / 8; ++i) {
+          const uint4 t = p[i];
+          const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __half22float2(h[q]);
+            xv[8 * i + 2 * q] = f.x; xv[8 * i + 2 * q + 1] = f.y;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPS; ++i) xv[i] = 0.f;
+    }
+    float mx = 0.f, sm = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPS; ++i) { mx = fmaxf(mx, fabsf(xv[i])); sm += xv[i]; }
+#pragma unroll
+    for (int o = 1; o < LPG; o <<= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      sm += __shfl_xor_sync(0xffffffffu, sm, o);
+    }
+    const int c = scale_exp_i8(mx);
+    if (on && (lane % LPG) == 0) {
+      T.xsum[row / LPG] = sm;
+      T.fin[row / LPG] = pow2i(-c);
+    }
+    if (on) {
+      constexpr int QB = CPB >= 4 ? 4 : CPB;
+      const float fb = pow2i(c);
+#pragma unroll
+      for (int q0 = 0; q0 < CPB; q0 += QB) {
+        uint32_t pl[3][QB];
+#pragma unroll
+        for (int qq = 0; qq < QB; ++qq) {
+          const int q = q0 + qq;
+          const float f = fb * (1.0f / static_cast<float>(1 << (B * q)));
+          uint32_t e[4];
+#pragma unroll
+          for (int y = 0; y < 4; ++y) e[y] = digits_word(xv[y * CPB + q], f);
+          const uint32_t x01 = __byte_perm(e[0], e[1], 0x5410), x23 = __byte_perm(e[2], e[3], 0x5410);
+          pl[0][qq] = __byte_perm(x01, x23, 0x6420) ^ 0x80808080u;
+          pl[1][qq] = __byte_perm(x01, x23, 0x7531) ^ 0x80808080u;
+          const uint32_t t =
+              __byte_perm(__byte_perm(e[0], e[1], 0x0062), __byte_perm(e[2], e[3], 0x0062), 0x5410) ^ 0x40404040u;
+          pl[2][qq] = t | ((t & 0x40404040u) << 1);  // sign-extend the 7-bit top digit
+        }
+#pragma unroll
+        for (int p = 0; p < 3; ++p) {
+          uint32_t* dst = T.tab + p * ps + row * CPB + q0;
+          if (QB == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(pl[p][0], pl[p][1], pl[p][2], pl[p][3]);
+          else *reinterpret_cast<uint2*>(dst) = make_uint2(pl[p][0], pl[p][1]);
+        }
+      }
+    }
+  }
+}
+
+// 3-bit tables: tab0[row][16 halves] holds the pre-scaled activations of the codes of packed row
+// `row` that belong to the row's first group, tab1[group][16 halves] those of the row that
+// straddles into `group` from the group before; half 2q+hi = code q + 5*hi of the row.
+// A warp takes up to four groups at a time so that their loads are in flight together.
+__device__ __forceinline__ int b3_rows(int K) { return (K + 9) / 10; }
+__device__ __forceinline__ void build_b3(Tables& T, const void* x, bool xf32, int K, unsigned need, const int* flags,
+                                         int* err, int warp, int lane) {
+  const int rows = b3_rows(K), ngroups = K / kGroup;
+  uint32_t* tab1w = T.tab + rows * 8;
+  const int words = rows * 8 + ngroups * 8;
+  for (int i = warp * 32 + lane; i < words; i += kConsThreads) T.tab[i] = 0u;
+  bar_consumers();
+  __half* tab0 = reinterpret_cast<__half*>(T.tab);
+  __half* tab1 = reinterpret_cast<__half*>(tab1w);
+  int taken = 0, gq = 0;
+  while (gq < ngroups) {
+    int mine[4], nmine = 0;
+    for (; gq < ngroups && nmine < 4; ++gq) {
+      if (gq / 5 < 32 && !((need >> (gq / 5)) & 1u)) continue;
+      if ((taken++ % kCons) != warp) continue;
+      mine[nmine++] = gq;
+    }
+    float xv[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (u < nmine) {
+        wait_groups(flags, mine[u], mine[u] + 1, err);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const size_t k = static_cast<size_t>(mine[u]) * kGroup + i * 32 + lane;
+          xv[u][i] = xf32 ? __ldcg(static_cast<const float*>(x) + k) : __half2float(static_cast<const __half*>(x)[k]);
+        }
+      }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (u < nmine) {
+        const int gg = mine[u];
+        float mx = 0.f, sm = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { mx = fmaxf(mx, fabsf(xv[u][i])); sm += xv[u][i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+          sm += __shfl_xor_sync(0xffffffffu, sm, o);
+        }
+        const int c = scale_exp_b3(mx);
+        if (lane == 0) {
+          T.xsum[gg] = sm;
+          T.fin[gg] = pow2i(24 - c);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int e = gg * kGroup + i * 32 + lane;
+          const int row = e / 10, j = e - row * 10;
+          const int hi = j >= 5 ? 1 : 0, q = j - 5 * hi;
+          const int pos = 3 * (q < 3 ? q : q - 3);
+          const __half v = __float2half_rn(xv[u][i] * pow2i(c - pos));
+          if (gg == ((row * 10) >> 7)) tab0[row * 16 + 2 * q + hi] = v;
+          else tab1[gg * 16 + 2 * q + hi] = v;
+        }
+      }
+  }
+}
+
+// All consumer warps: wait until nobody reads the old table, build the new one, publish it.
+// `need`: bit q set = quantum q (4 groups; 5 for 3-bit) of the vector is wanted.  `flags`: one
+// word per group that turns non-zero when the group's slice of the vector exists (h in phase 1),
+// or nullptr.
+__device__ __noinline__ void build_table(Tables* T, const void* x, int xf32, int K, int B, unsigned need, const int* flags,
+                                         int* err, int warp, int lane) {
+  bar_consumers();
+  if (B == 1) build_i8<1>(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
+  else if (B == 2) build_i8<2>(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
+  else if (B == 3) build_b3(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
+  else build_i8<4>(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
+  bar_consumers();
+}
+
+// ---- router (same arithmetic as route_kernel: identical ids and weights in every CTA) --------
+__device__ __forceinline__ float dot8h(const uint4& a, const uint4& b) {
+  const __half* pa = reinterpret_cast<const __half*>(&a);
+  const __half* pb = reinterpret_cast<const __half*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s = fmaf(__half2float(pa[i]), __half2float(pb[i]), s);
+  return s;
+}
+__device__ __forceinline__ float round_h(float v) { return __half2float(__float2half_rn(v)); }
+
+__device__ void route_cta(Smem& S, const FusedParams& P) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int E = P.E, D = P.D, A = P.A, mode = P.route_mode;
+  int parts = E >= 32 ? 1 : 32 / E;
+  parts = parts > 8 ? 8 : parts;
+  while (parts > 1 && (D % (parts * 256)) != 0) parts >>= 1;
+  const int seg = D / parts;
+  for (int task = warp; task < E * parts; task += kWarps) {
+    const int e = task / parts, sg = task - e * parts;
+    const __half* ge = P.gate + static_cast<size_t>(e) * D + static_cast<size_t>(sg) * seg;
+    const __half* xs = P.x + static_cast<size_t>(sg) * seg;
+    float s = 0.f;
+    for (int k0 = 0; k0 < seg; k0 += 4 * 256) {
+      uint4 gq[4], xq[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int k = k0 + (i * 32 + lane) * 8;
+        if (k < seg) {
+          gq[i] = *reinterpret_cast<const uint4*>(ge + k);
+          xq[i] = *reinterpret_cast<const uint4*>(xs + k);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (k0 + (i * 32 + lane) * 8 < seg) s += dot8h(xq[i], gq[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) S.part_sum[e][sg] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x < E) {
+    float s = 0.f;
+    for (int q = 0; q < parts; ++q) s += S.part_sum[threadIdx.x][q];
+    if (mode != 2) s = round_h(s);
+    S.logit[threadIdx.x] = s;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float p = lane < E ? S.logit[lane] : -INFINITY;
+  float mx = p;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  p = lane < E ? expf(p - mx) : 0.f;
+  float sum = p;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  p = p / sum;
+  if (mode == 0) p = round_h(p);
+  if (lane >= E) p = -1.f;
+  float my_w = 0.f;
+  int my_i = 0;
+  for (int a = 0; a < A; ++a) {
+    float bv = p > -2.f ? p : -2.f;
+    int bi = p > -2.f ? lane : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == a) { my_w = bv; my_i = bi; }
+    if (lane == bi) p = -3.f;
+  }
+  float tot = 0.f;
+  for (int a = 0; a < A; ++a) tot += __shfl_sync(0xffffffffu, my_w, a);
+  if (mode == 0) tot = round_h(tot);
+  if (lane < A) {
+    const __half wv = __float2half_rn(P.renorm ? my_w / tot : my_w);
+    S.sel_e[lane] = my_i;
+    S.sel_w[lane] = wv;
+    if (blockIdx.x == 0) {
+      P.idx[lane] = my_i;
+      P.w[lane] = wv;
+    }
+  }
+}
+
+// ---- plan (warp 0) ----------------------------------------------------------------------------
+__device__ void make_plan(Smem& S, const FusedParams& P) {
+  const int lane = threadIdx.x & 31;
+  const int Sn = P.S;
+  // slots
+  int Fs = 0, b1 = 1, b2 = 1;
+  if (lane < Sn) {
+    SlotInfo I;
+    if (lane < P.A) {
+      int e = S.sel_e[lane];
+      e = e < 0 ? 0 : (e >= P.E ? P.E - 1 : e);
+      const bool pre = P.E <= kMetaE;  // tables staged in shared memory ahead of the dependency wait
+      b1 = clamp_bits(pre ? S.emeta[0][e] : P.nbits1[e]);
+      b2 = clamp_bits(pre ? S.emeta[1][e] : P.nbits2[e]);
+      Fs = P.F;
+      const size_t o1 = static_cast<size_t>(pre ? S.emeta[2][e] : P.wqs1[e]);
+      const size_t o2 = static_cast<size_t>(pre ? S.emeta[3][e] : P.wqs2[e]);
+      const size_t z1 = P.zss1 ? static_cast<size_t>(pre ? S.emeta[4][e] : P.zss1[e])
+                               : static_cast<size_t>(e) * (P.D / kGroup) * P.F;
+      const size_t z3 = P.zss3 ? static_cast<size_t>(pre ? S.emeta[5][e] : P.zss3[e]) : z1;
+      const size_t z2 = P.zss2 ? static_cast<size_t>(pre ? S.emeta[6][e] : P.zss2[e])
+                               : static_cast<size_t>(e) * (P.F / kGroup) * P.D;
+      I.wq[0] = P.w1.wq + o1; I.wq[1] = P.w3.wq + o1; I.wq[2] = P.w2.wq + o2;
+      I.sc[0] = P.w1.sc + z1; I.zr[0] = P.w1.zr + z1;
+      I.sc[1] = P.w3.sc + z3; I.zr[1] = P.w3.zr + z3;
+      I.sc[2] = P.w2.sc + z2; I.zr[2] = P.w2.zr + z2;
+    } else {
+      b1 = b2 = clamp_bits(P.sbits);
+      Fs = P.SF;
+      I.wq[0] = P.s1.wq; I.wq[1] = P.s3.wq; I.wq[2] = P.s2.wq;
+      I.sc[0] = P.s1.sc; I.zr[0] = P.s1.zr;
+      I.sc[1] = P.s3.sc; I.zr[1] = P.s3.zr;
+      I.sc[2] = P.s2.sc; I.zr[2] = P.s2.zr;
+    }
+    I.bits[0] = b1; I.bits[1] = b2;
+    I.F = Fs;
+    I.nq[0] = cdiv(P.D / kGroup, quantum_groups(b1));
+    I.nq[1] = cdiv(Fs / kGroup, quantum_groups(b2));
+    I.nch[0] = cdiv(Fs, 128);
+    I.nch[1] = cdiv(P.D, 128);
+    S.slot[lane] = I;
+  }
+  // exclusive prefix sums over the slots: h / partial offsets, pair counters, down quanta
+  int nch0 = lane < Sn ? cdiv(Fs, 128) : 0;
+  int fs = lane < Sn ? Fs : 0;
+  int nq1 = lane < Sn ? cdiv(Fs / kGroup, quantum_groups(b2)) : 0;
+  int in_nch = nch0, in_fs = fs, in_nq1 = nq1;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, in_nch, o), b = __shfl_up_sync(0xffffffffu, in_fs, o),
+              c = __shfl_up_sync(0xffffffffu, in_nq1, o);
+    if (lane >= o) { in_nch += a; in_fs += b; in_nq1 += c; }
+  }
+  const int pairs_total = __shfl_sync(0xffffffffu, in_nch, 31);
+  const int expected1 = __shfl_sync(0xffffffffu, in_nq1, 31);
+  const int nch1 = cdiv(P.D, 128);
+  const int base1 = 3 * pairs_total;
+  if (lane < Sn) {
+    SlotInfo& I = S.slot[lane];
+    I.hoff = in_fs - fs;
+    I.ctrb = in_nch - nch0;
+    I.colb[0] = 2 * (in_fs - fs);
+    I.colb[1] = lane * P.D;
+    I.maskb[0] = pairs_total + 2 * (in_nch - nch0);
+    I.maskb[1] = base1 + nch1 + lane * nch1;
+  }
+  if (lane == 0) {
+    S.pairs_total = pairs_total;
+    S.expected1 = expected1;
+    S.overflow = 0;
+  }
+  __syncwarp();
+  // ranges and parts of the two phases
+  int pbase = 0;
+  for (int ph = 0; ph < 2; ++ph) {
+    unsigned n_units = 0, cost = 1;
+    int nq = 1;
+    if (lane < Sn) {
+      const SlotInfo& I = S.slot[lane];
+      nq = I.nq[ph];
+      n_units = static_cast<unsigned>(I.nch[ph]) * (ph ? 1u : 2u) * nq;
+      cost = quantum_cost(I.bits[ph]);
+    }
+    const unsigned wgt = n_units * cost;
+    unsigned incl = wgt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const unsigned long long total = __shfl_sync(0xffffffffu, incl, 31);
+    const unsigned prefix = incl - wgt;
+    const unsigned lo = static_cast<unsigned>(total * blockIdx.x / gridDim.x);
+    const unsigned hi = static_cast<unsigned>(total * (blockIdx.x + 1) / gridDim.x);
+    unsigned ulo = lo <= prefix ? 0u : (lo - prefix + cost - 1) / cost;
+    unsigned uhi = hi <= prefix ? 0u : (hi - prefix + cost - 1) / cost;
+    ulo = min(ulo, n_units);
+    uhi = min(uhi, n_units);
+    const int np = uhi > ulo ? static_cast<int>((uhi - 1) / nq - ulo / nq + 1) : 0;
+    int inp = np;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inp, o);
+      if (lane >= o) inp += t;
+    }
+    const int np_total = __shfl_sync(0xffffffffu, inp, 31);
+    int pi = pbase + inp - np;
+    if (pbase + np_total > kMaxParts) {
+      if (lane == 0) S.overflow = 1;
+    } else if (np > 0) {
+      const SlotInfo& I = S.slot[lane];
+      const int B = I.bits[ph];
+      const int K = ph ? I.F : P.D, N = ph ? P.D : I.F;
+      const int ngroups = K / kGroup;
+      const int first_cm = static_cast<int>(ulo) / nq;
+      for (int k = 0; k < np; ++k, ++pi) {
+        const int cm = first_cm + k;
+        const int c = ph ? cm : (cm >> 1), m = ph ? 0 : (cm & 1), mi = ph ? 2 : m;
+        const int qa = max(static_cast<int>(ulo), cm * nq) - cm * nq;
+        const int qb = min(static_cast<int>(uhi), (cm + 1) * nq) - cm * nq;
+        PartDesc d;
+        const int n0 = c * 128;
+        d.w = I.wq[mi] + n0;
+        d.sc = I.sc[mi] + n0;
+        d.zr = I.zr[mi] + n0;
+        d.N = N; d.B = B; d.ngroups = ngroups;
+        d.kw = B == 3 ? b3_rows(K) : K / (32 / B);
+        if (B == 3) { d.run_lo = qa; d.run_hi = min(qb, nq); }
+        else { d.run_lo = 2 * qa; d.run_hi = min(2 * qb, cdiv(ngroups, 2)); }
+        d.ncols = min(128, N - n0);
+        d.tab = ph ? 8 + lane : B;
+        d.phase = ph; d.s = lane; d.c = c;
+        d.qa = qa; d.qb = qb;
+        if (ph) {
+          d.ctr = base1 + c;
+          d.expected = expected1;
+          d.mask = I.maskb[1] + c;
+          d.colp = I.colb[1] + n0;
+        } else {
+          d.ctr = I.ctrb + c;  // index of a 64-bit word
+          d.expected = 2 * nq;
+          d.mask = m;          // phase 0: which half of the slot set this part's bit goes to
+          d.colp = I.colb[0] + m * I.F + n0;
+        }
+        S.parts[pi] = d;
+      }
+    }
+    pbase += np_total;
+    if (ph == 0 && lane == 0) S.n_parts0 = pbase;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    const int n = S.overflow ? 0 : pbase;
+    int runs = 0;
+    for (int p = 0; p < n; ++p) {
+      S.parts[p].roff = runs % kLanes;
+      runs += S.parts[p].run_hi - S.parts[p].run_lo;
+    }
+    S.n_parts = n;
+  }
+}
+
+// ---- the load side of a consumer warp: walks the warp's tasks ahead of the compute side ------
+// A flush run (two groups; five for 3-bit) is a sequence of ring tasks: nt weight tasks of 4
+// packed rows x 128 columns, then nm "meta" tasks, task k carrying the scales | offsets
+// (256 + 256 bytes per group) of the run's groups 4k .. 4k+3.  The run is folded when its last
+// meta task arrives, reading the scales straight from the ring.
+struct Loader {
+  const uint32_t* w;    // lane's 16 bytes in row 0 of the next weight task
+  const uint32_t* safe; // a valid address of the part's matrix for the zero-filled copies
+  const __half* m;      // lane's 16 bytes of scales (lanes 0..15) / offsets (16..31) of group 0 of the run
+  int i, nt, ntot;      // next task of the run; weight tasks; weight + meta tasks
+  int N;                // row pitch of the part's matrix (words, = halves of the scale rows)
+  int rows_left;        // 3-bit: valid packed rows from the next weight task on (other widths: large)
+  int ng;               // groups of the run
+  int run, run_hi, p;   // current run, end of the part's runs, part
+  int slot;             // ring slot of the next task
+  uint32_t ring;        // shared address of the warp's ring
+  uint32_t roff[4];     // lane's position inside a weight task, per row
+};
+
+__device__ __forceinline__ int run_groups(int B, int run, int ngroups) {
+  return B == 3 ? min(5, ngroups - 5 * run) : min(2, ngroups - 2 * run);
+}
+__device__ __forceinline__ int run_weight_tasks(int B, int run, int ngroups, int kw) {
+  if (B == 3) {
+    const int rows = min(64, kw - 64 * run);
+    return 2 * ((rows + 7) >> 3);
+  }
+  return min(2, ngroups - 2 * run) * B;
+}
+// first run of run lane kq in a part
+__device__ __forceinline__ int first_run(const PartDesc& d, int kq) { return d.run_lo + (kq + kLanes - d.roff) % kLanes; }
+
+// Ring position of the 16 bytes of column quad q (4 columns) of task row r: quads are permuted
+// inside groups of eight so that lanes reading different rows hit different banks.
+__device__ __forceinline__ int ring_off(int r, int q) { return r * 512 + (((q & 24) | ((q ^ (2 * r)) & 7)) << 4); }
+
+__device__ __forceinline__ void cp_async16s(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+// Move the loader to the first task of its next run.
+__device__ __forceinline__ void loader_next_run(Loader* Lp, const Smem* Sp, int kq, int lane, int first) {
+  Loader& L = *Lp;
+  const Smem& S = *Sp;
+  if (!first) L.run += kLanes;
+  while (L.p < 0 || L.run >= L.run_hi) {
+    if (++L.p >= S.n_parts) { L.ntot = 0; L.i = 0; return; }
+    const PartDesc& d = S.parts[L.p];
+    L.run_hi = d.run_hi;
+    L.run = first_run(d, kq);
+  }
+  const PartDesc& d = S.parts[L.p];
+  const int B = d.B;
+  L.N = d.N;
+  L.ng = run_groups(B, L.run, d.ngroups);
+  L.nt = run_weight_tasks(B, L.run, d.ngroups, d.kw);
+  L.ntot = L.nt + ((L.ng + 3) >> 2);
+  L.i = 0;
+  const int row0 = (B == 3 ? 64 : 8 * B) * L.run;
+  L.rows_left = B == 3 ? d.kw - row0 : (1 << 30);
+  L.w = d.w + static_cast<size_t>(row0) * d.N + 4 * lane;
+  L.safe = d.w + 4 * lane;
+  L.m = ((lane & 16) ? d.zr : d.sc) + static_cast<size_t>((B == 3 ? 5 : 2) * L.run) * d.N + 8 * (lane & 15);
+}
+
+// Issue the copies of the loader's next task (one commit group per call, empty when the warp
+// has run out of tasks) and step to the task after it.
+__device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, int lane) {
+  if (L.i < L.ntot) {
+    const uint32_t dst = L.ring + L.slot * kSlotBytes;
+    if (L.i < L.nt) {
+      // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
+      const uint32_t* src = L.rows_left > 0 ? L.w : L.safe;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        cp_async16s(dst + L.roff[r], src, r < L.rows_left ? 16 : 0);
+        if (r < 3 && r + 1 < L.rows_left) src += L.N;
+      }
+      L.w += 4 * static_cast<size_t>(L.N);
+      L.rows_left -= 4;
+    } else {
+      // group h of the four: lanes 0..15 copy its 256 bytes of scales, lanes 16..31 its offsets
+      const int g0 = 4 * (L.i - L.nt);
+      const __half* src = L.m + static_cast<size_t>(g0) * L.N;
+#pragma unroll
+      for (int h = 0; h < 4; ++h)
+        if (g0 + h < L.ng) {
+          cp_async16s(dst + 512 * h + 16 * lane, src, 16);
+          src += L.N;
+        }
+    }
+    if (++L.i == L.ntot) loader_next_run(&L, &S, kq, lane, 0);
+  }
+  cp_async_commit();
+  L.slot = L.slot + 1 == kRing ? 0 : L.slot + 1;
+}
+
+// ---- compute side -------------------------------------------------------------------------------
+struct RunState {
+  int acc[4][2][4];   // [column quad group j][tile s][C fragment]: columns 4(g+8j) + 2s, + 2s+1
+  float vs[4][2][2];  // running sums of those two columns over the runs of the part
+};
+
+__device__ __forceinline__ void unpack4(const uint2& r, float (&f)[4]) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+// Weight task of a 1/2/4-bit run: `wp` = lane's row c, quad g in the ring slot, `bp` = lane's B
+// operand words of that row (nullptr: this lane's MMA column is not fed by the task's group).
+template <int B>
+__device__ __forceinline__ void task_i8(RunState& R, const unsigned char* wp, const uint32_t* bp) {
+  using F = I8<B>;
+  constexpr int CPB = F::kCpb;
+  uint32_t bf[CPB];
+#pragma unroll
+  for (int q = 0; q < CPB; ++q) bf[q] = 0u;
+  if (bp) {
+    if (CPB >= 4) {
+#pragma unroll
+      for (int q4 = 0; q4 < CPB / 4; ++q4) {
+        const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
+        bf[4 * q4] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
+      }
+    } else {
+      const uint2 t = *reinterpret_cast<const uint2*>(bp);
+      bf[0] = t.x; bf[1] = t.y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 w = *reinterpret_cast<const uint4*>(wp + 128 * j);
+    const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int mm = 0; mm < CPB / 2; ++mm)
+#pragma unroll
+      for (int s = 0; s < 2; ++s)
+        mma_u8s8(R.acc[j][s], F::operand(wv[2 * s], 2 * mm), F::operand(wv[2 * s + 1], 2 * mm),
+                 F::operand(wv[2 * s], 2 * mm + 1), F::operand(wv[2 * s + 1], 2 * mm + 1), bf[2 * mm], bf[2 * mm + 1]);
+  }
+}
+
+// Fold a 1/2/4-bit run into the running sums; `mp` = the run's meta task in the ring.
+// C columns 2c, 2c+1 hold digit planes 2(c&1), 2(c&1)+1 of group (c >> 1) of the pair.
+__device__ __forceinline__ void fold_i8(RunState* Rp, const Tables* Tp, const unsigned char* mp, int run, int ng, int lane) {
+  RunState& R = *Rp;
+  const Tables& T = *Tp;
+  const int g = lane >> 2, c = lane & 3;
+  const int gu = c >> 1;
+  if (gu < ng) {
+    const int grp = 2 * run + gu;
+    const float f0 = T.fin[grp] * ((c & 1) ? 65536.0f : 1.0f), f1 = f0 * 256.0f;
+    const float xs = (c & 1) ? 0.f : T.xsum[grp];  // the offset term z * sum(x), once per group and column
+    const unsigned char* gp = mp + 512 * gu + 8 * g;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float sc[4], zr[4];
+      unpack4(*reinterpret_cast<const uint2*>(gp + 64 * j), sc);
+      unpack4(*reinterpret_cast<const uint2*>(gp + 256 + 64 * j), zr);
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const float ta = fmaf(f1, __int2float_rn(R.acc[j][s][1]), f0 * __int2float_rn(R.acc[j][s][0]));
+        const float tb = fmaf(f1, __int2float_rn(R.acc[j][s][3]), f0 * __int2float_rn(R.acc[j][s][2]));
+        R.vs[j][s][0] += fmaf(sc[2 * s], ta, zr[2 * s] * xs);
+        R.vs[j][s][1] += fmaf(sc[2 * s + 1], tb, zr[2 * s + 1] * xs);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) R.acc[j][s][e] = 0;
+}
+
+// 3-bit: merge the two 15-bit halves of a word into fp16x2 lanes, then mask out code pairs.
+__device__ __forceinline__ uint32_t b3_merge(uint32_t w) { return (w & 0x00007fffu) | ((w << 1) & 0x7fff0000u); }
+__device__ __forceinline__ uint32_t b3_operand(uint32_t t, int q) {
+  return q < 3 ? (t & (0x00070007u << (3 * q))) : ((t >> 9) & (0x00070007u << (3 * (q - 3))));
+}
+
+// Weight tasks come in pairs (8 packed rows): the odd task of a pair does the work, lane c takes
+// rows 2c and 2c+1 of the pair, i.e. rows of the previous ring slot for c < 2.
+__device__ __forceinline__ void task_b3(RunState& R, const Tables& T, const uint32_t* zero_row, const unsigned char* prevp,
+                                        const unsigned char* slotp, int run, int i, int K, int kw, int ngroups, int lane) {
+  const int g = lane >> 2, c = lane & 3;
+  const int rows3 = b3_rows(K);
+  uint32_t bf[10];
+  const unsigned char* wp[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int lr = 2 * c + r;  // row inside the pair of tasks
+    const int row = 64 * run + 8 * (i >> 1) + lr;
+    wp[r] = (lr < 4 ? prevp : slotp) + ring_off(lr & 3, g);
+    const int d0 = (row * 10) >> 7, d1 = (row * 10 + 9) >> 7;
+    const int dl = d0 - 5 * run;
+    const uint32_t* bp = zero_row;
+    if (row < kw) {
+      if (g == dl) bp = T.tab + row * 8;
+      else if (g == dl + 1 && d1 != d0 && d1 < ngroups) bp = T.tab + rows3 * 8 + d1 * 8;
+    }
+    const uint4 t4 = *reinterpret_cast<const uint4*>(bp);
+    bf[5 * r + 0] = t4.x; bf[5 * r + 1] = t4.y; bf[5 * r + 2] = t4.z; bf[5 * r + 3] = t4.w;
+    bf[5 * r + 4] = bp[4];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t mw[2][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint4 w = *reinterpret_cast<const uint4*>(wp[r] + 128 * j);
+      mw[r][0] = b3_merge(w.x); mw[r][1] = b3_merge(w.y); mw[r][2] = b3_merge(w.z); mw[r][3] = b3_merge(w.w);
+    }
+#pragma unroll
+    for (int mm = 0; mm < 5; ++mm)
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int s0 = 2 * mm, s1 = 2 * mm + 1;
+        const uint32_t a0 = s0 < 5 ? b3_operand(mw[0][2 * s], s0) : b3_operand(mw[1][2 * s], s0 - 5);
+        const uint32_t a1 = s0 < 5 ? b3_operand(mw[0][2 * s + 1], s0) : b3_operand(mw[1][2 * s + 1], s0 - 5);
+        const uint32_t a2 = s1 < 5 ? b3_operand(mw[0][2 * s], s1) : b3_operand(mw[1][2 * s], s1 - 5);
+        const uint32_t a3 = s1 < 5 ? b3_operand(mw[0][2 * s + 1], s1) : b3_operand(mw[1][2 * s + 1], s1 - 5);
+        mma_f16(R.acc[j][s], a0, a1, a2, a3, bf[s0], bf[s1]);
+      }
+  }
+}
+
+// Fold a 3-bit run: C column d of a tile holds run-local group d; groups 0..3 sit in the first
+// meta task (`m0`), group 4 in the second (`m1`).
+__device__ __forceinline__ void fold_b3(RunState* Rp, const Tables* Tp, const unsigned char* m0, const unsigned char* m1,
+                                     int run, int ng, int lane) {
+  RunState& R = *Rp;
+  const Tables& T = *Tp;
+  const int g = lane >> 2, c = lane & 3;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    const int d = 2 * c + p;
+    if (d < ng) {
+      const int grp = 5 * run + d;
+      const float fin = T.fin[grp], xs = T.xsum[grp];
+      const unsigned char* gp = (d < 4 ? m0 : m1) + 512 * (d & 3) + 8 * g;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float sc[4], zr[4];
+        unpack4(*reinterpret_cast<const uint2*>(gp + 64 * j), sc);
+        unpack4(*reinterpret_cast<const uint2*>(gp + 256 + 64 * j), zr);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          R.vs[j][s][0] += fmaf(sc[2 * s] * fin, __int_as_float(R.acc[j][s][p]), zr[2 * s] * xs);
+          R.vs[j][s][1] += fmaf(sc[2 * s + 1] * fin, __int_as_float(R.acc[j][s][2 + p]), zr[2 * s + 1] * xs);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) R.acc[j][s][e] = 0;
+}
+
+// The compute side's position in its ring.
+struct Cursor {
+  const unsigned char* ring;  // the warp's ring
+  int slot;                   // slot of the next task
+};
+__device__ __forceinline__ const unsigned char* cursor_take(Cursor& C) {
+  cp_async_wait<kRing - 2>();
+  __syncwarp();
+  const unsigned char* p = C.ring + C.slot * kSlotBytes;
+  C.slot = C.slot + 1 == kRing ? 0 : C.slot + 1;
+  return p;
+}
+
+// All runs of run lane kq in a 1/2/4-bit part.
+template <int B>
+__device__ __forceinline__ void part_i8(RunState& R, Loader& L, Cursor& C, const Smem& S, const PartDesc& d, int kq, int lane) {
+  using F = I8<B>;
+  const int g = lane >> 2, c = lane & 3;
+  const int K = d.ngroups * kGroup;
+  const int woff = ring_off(c, g);
+  // this lane's MMA column: digit plane (g & 3) of the first (g < 4) or second group of a run; column 3 / 7 stays empty
+  const uint32_t* plane = S.T.tab + (g & 3) * F::plane_stride(K) + c * F::kCpb;
+  const bool feeds = (g & 3) < 3;
+  const int run_hi = d.run_hi;
+#pragma unroll 1
+  for (int run = first_run(d, kq); run < run_hi; run += kLanes) {
+    const int ng = min(2, d.ngroups - 2 * run);
+    const uint32_t* bp = plane + 8 * B * run * F::kCpb;
+#pragma unroll 1
+    for (int gi = 0; gi < ng; ++gi) {
+      const bool on = feeds && (g >> 2) == gi;
+#pragma unroll 1
+      for (int ii = 0; ii < B; ++ii) {
+        const unsigned char* slotp = cursor_take(C);
+        task_i8<B>(R, slotp + woff, on ? bp : nullptr);
+        bp += 4 * F::kCpb;
+        loader_step(L, S, kq, lane);
+      }
+    }
+    const unsigned char* mp = cursor_take(C);
+    fold_i8(&R, &S.T, mp, run, ng, lane);
+    loader_step(L, S, kq, lane);
+  }
+}
+
+__device__ __forceinline__ void part_b3(RunState& R, Loader& L, Cursor& C, const Smem& S, const PartDesc& d,
+                                        const uint32_t* zero_row, int kq, int lane) {
+  const int K = d.ngroups * kGroup;
+  const int run_hi = d.run_hi;
+#pragma unroll 1
+  for (int run = first_run(d, kq); run < run_hi; run += kLanes) {
+    const int ng = min(5, d.ngroups - 5 * run);
+    const int nt = run_weight_tasks(3, run, d.ngroups, d.kw);
+    const unsigned char* prev = nullptr;
+#pragma unroll 1
+    for (int i = 0; i < nt; ++i) {
+      const unsigned char* slotp = cursor_take(C);
+      if (i & 1) task_b3(R, S.T, zero_row, prev, slotp, run, i, K, d.kw, d.ngroups, lane);
+      prev = slotp;
+      __syncwarp();  // every lane is done with `prev` of the last pair before its slot is refilled
+      loader_step(L, S, kq, lane);
+    }
+    const unsigned char* m0 = cursor_take(C);
+    const unsigned char* m1 = m0;
+    if (ng > 4) {
+      __syncwarp();
+      loader_step(L, S, kq, lane);
+      m1 = cursor_take(C);
+    }
+    fold_b3(&R, &S.T, m0, m1, run, ng, lane);
+    __syncwarp();
+    loader_step(L, S, kq, lane);
+  }
+}
+
+__device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zero_row, int* err) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kq = warp;
+  const int g = lane >> 2, c = lane & 3;
+  Loader L;
+  L.p = -1; L.run = 0; L.run_hi = 0; L.i = 0; L.nt = 0; L.ntot = 0; L.N = 0; L.rows_left = 0; L.ng = 0;
+  L.w = nullptr; L.m = nullptr; L.safe = nullptr;
+  L.slot = 0;
+  L.ring = smem_u32(S.ring[warp][0]);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) L.roff[r] = ring_off(r, lane);
+  loader_next_run(&L, &S, kq, lane, 1);
+  // the weights do not depend on the tables: fill the ring first
+#pragma unroll 1
+  for (int k = 0; k < kRing - 1; ++k) loader_step(L, S, kq, lane);
+  Cursor C;
+  C.ring = S.ring[warp][0];
+  C.slot = 0;
+  RunState R;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) R.acc[j][s][e] = 0;
+      R.vs[j][s][0] = 0.f; R.vs[j][s][1] = 0.f;
+    }
+
+  int cur_tab = -1;
+  const int n_parts = S.n_parts;
+#pragma unroll 1
+  for (int p = 0; p < n_parts; ++p) {
+    const PartDesc& d = S.parts[p];
+    const int B = d.B;
+    if (d.tab != cur_tab) {
+      const void* xsrc = d.phase ? static_cast<const void*>(P.h + S.slot[d.s].hoff) : static_cast<const void*>(P.x);
+      // phase 1 needs the digits of the quanta this CTA's parts of the slot cover, not the whole vector
+      unsigned need = 0xffffffffu;
+      if (d.phase) {
+        need = 0u;
+        for (int pp = p; pp < n_parts && S.parts[pp].tab == d.tab; ++pp)
+          need |= (S.parts[pp].qb >= 32 ? 0xffffffffu : ((1u << S.parts[pp].qb) - 1u)) & ~((1u << S.parts[pp].qa) - 1u);
+      }
+      // the h chunks of a slot are the reduction groups of its down projection: their flags gate the build
+      const int* flags = d.phase ? P.counters + 2 * S.pairs_total + S.slot[d.s].ctrb : nullptr;
+      build_table(&S.T, xsrc, d.phase, d.ngroups * kGroup, B, need, flags, err, warp, lane);
+      cur_tab = d.tab;
+    }
+    if (B == 1) part_i8<1>(R, L, C, S, d, kq, lane);
+    else if (B == 2) part_i8<2>(R, L, C, S, d, kq, lane);
+    else if (B == 4) part_i8<4>(R, L, C, S, d, kq, lane);
+    else part_b3(R, L, C, S, d, zero_row, kq, lane);
+    // end of the part: fold the MMA columns of the four lanes of a row, hand the columns to the finisher
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int s = 0; s < 2; ++s)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          R.vs[j][s][e] += __shfl_xor_sync(0xffffffffu, R.vs[j][s][e], 1);
+          R.vs[j][s][e] += __shfl_xor_sync(0xffffffffu, R.vs[j][s][e], 2);
+        }
+    const int rs = p % kRedSlots;
+    mbar_wait(&S.redempty[rs], ((p / kRedSlots) & 1) ^ 1, err, kErrRedEmpty);
+    if (c == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<float4*>(&S.red[rs][kq][4 * (g + 8 * j)]) =
+            make_float4(R.vs[j][0][0], R.vs[j][0][1], R.vs[j][1][0], R.vs[j][1][1]);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&S.redfull[rs]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int s = 0; s < 2; ++s) { R.vs[j][s][0] = 0.f; R.vs[j][s][1] = 0.f; }
+  }
+  cp_async_wait<0>();
+}
+
+// ---- finisher ---------------------------------------------------------------------------------
+// Sum the partial slots of columns n..n+3 in slice order and restore them to zero; `slot_set`
+// says which slots hold a partial (one bit per part, at the part's first quantum).
+__device__ __noinline__ float4 drain_slots(float* src, size_t c_total, const unsigned* slot_set, int slices) {
+  constexpr int kBatch = 4;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (slices <= 32) {
+    unsigned m = __ldcg(slot_set);
+    while (m) {
+      float4 t[kBatch];
+      float4* q[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        q[i] = nullptr;
+        if (m) {
+          const int s = __ffs(m) - 1;
+          m &= m - 1;
+          q[i] = reinterpret_cast<float4*>(src + static_cast<size_t>(s) * c_total);
+          t[i] = __ldcg(q[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i)
+        if (q[i]) {
+          sum.x += t[i].x; sum.y += t[i].y; sum.z += t[i].z; sum.w += t[i].w;
+          __stcg(q[i], make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+    }
+    return sum;
+  }
+  for (int s0 = 0; s0 < slices; s0 += kBatch) {
+    float4 t[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (s0 + i < slices) t[i] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(s0 + i) * c_total));
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i)
+      if (s0 + i < slices) {
+        sum.x += t[i].x; sum.y += t[i].y; sum.z += t[i].z; sum.w += t[i].w;
+        __stcg(reinterpret_cast<float4*>(src + static_cast<size_t>(s0 + i) * c_total), make_float4(0.f, 0.f, 0.f, 0.f));
+      }
+  }
+  return sum;
+}
+
+// Two jobs at once (gate and up partials of a column chunk), slot sets given by value: the
+// loads of both jobs are in flight together; each job is summed in slice order.
+__device__ __forceinline__ void drain_pair(float* sa, float* sb, size_t c_total, unsigned ma, unsigned mb, float4& a,
+                                           float4& b) {
+  a = make_float4(0.f, 0.f, 0.f, 0.f);
+  b = a;
+  const float4 zero = a;
+  while (ma | mb) {
+    float4* qa = nullptr;
+    float4* qb = nullptr;
+    float4 ta = zero, tb = zero;
+    if (ma) {
+      qa = reinterpret_cast<float4*>(sa + static_cast<size_t>(__ffs(ma) - 1) * c_total);
+      ma &= ma - 1;
+      ta = __ldcg(qa);
+    }
+    if (mb) {
+      qb = reinterpret_cast<float4*>(sb + static_cast<size_t>(__ffs(mb) - 1) * c_total);
+      mb &= mb - 1;
+      tb = __ldcg(qb);
+    }
+    if (qa) { a.x += ta.x; a.y += ta.y; a.z += ta.z; a.w += ta.w; __stcg(qa, zero); }
+    if (qb) { b.x += tb.x; b.y += tb.y; b.z += tb.z; b.w += tb.w; __stcg(qb, zero); }
+  }
+}
+
+__device__ __forceinline__ void store_half4(__half* dst, const float4& v) {
+  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&lo);
+  o.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = o;
+}
+__device__ __forceinline__ float4 round_half4(const float4& v) {
+  return make_float4(round_h(v.x), round_h(v.y), round_h(v.z), round_h(v.w));
+}
+
+// Finisher warp f takes the parts p = f, f + kFin, ...: it owns reduction slot f.
+__device__ void finisher_role(Smem& S, const FusedParams& P, int* err) {
+  const int lane = threadIdx.x & 31;
+  const int n_parts = S.n_parts;
+  unsigned* cw = reinterpret_cast<unsigned*>(P.counters);
+  const int rs = (threadIdx.x >> 5) - kCons;
+  for (int p = rs; p < n_parts; p += kFin) {
+    const PartDesc& d = S.parts[p];
+    mbar_wait(&S.redfull[rs], (p / kRedSlots) & 1, err, kErrRedFull);
+    float4 r = *reinterpret_cast<const float4*>(&S.red[rs][0][4 * lane]);
+#pragma unroll
+    for (int q = 1; q < kLanes; ++q) {
+      const float4 t = *reinterpret_cast<const float4*>(&S.red[rs][q][4 * lane]);
+      r.x += t.x; r.y += t.y; r.z += t.z; r.w += t.w;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&S.redempty[rs]);
+
+    const bool col_on = 4 * lane < d.ncols;
+    const size_t ct = static_cast<size_t>(P.c_total);
+    if (col_on) __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(d.qa) * ct + d.colp + 4 * lane), r);
+    const int n = d.c * 128 + 4 * lane;
+    if (d.phase == 0) {
+      // One 64-bit word per (slot, column chunk): arrivals in the low half, the set of partial
+      // slots in use in the high half (gate: bits 0..15, up: bits 16..31), so that the CTA that
+      // completes the pair learns both from the atomic it has to issue anyway.
+      __threadfence();
+      __syncwarp();
+      unsigned lo = 0, hi = 0;
+      if (lane == 0) {
+        unsigned long long* c64 = reinterpret_cast<unsigned long long*>(P.counters) + d.ctr;
+        const unsigned long long mine = 1ull << (32 + 16 * d.mask + d.qa);
+        const unsigned long long old = atomicAdd(c64, static_cast<unsigned long long>(d.qb - d.qa) | mine);
+        lo = static_cast<unsigned>(old) + static_cast<unsigned>(d.qb - d.qa);
+        hi = static_cast<unsigned>((old | mine) >> 32);
+        if (static_cast<int>(lo) == d.expected) *c64 = 0ull;
+      }
+      lo = __shfl_sync(0xffffffffu, lo, 0);
+      hi = __shfl_sync(0xffffffffu, hi, 0);
+      if (static_cast<int>(lo) != d.expected) continue;
+      __threadfence();
+      const SlotInfo& I = S.slot[d.s];
+      if (col_on) {
+        float4 a, b;
+        drain_pair(P.partial + I.colb[0] + n, P.partial + I.colb[0] + I.F + n, ct, hi & 0xffffu, hi >> 16, a, b);
+        a = round_half4(a);
+        b = round_half4(b);
+        *reinterpret_cast<float4*>(P.h + I.hoff + n) =
+            make_float4(silu_f32(a.x) * b.x, silu_f32(a.y) * b.y, silu_f32(a.z) * b.z, silu_f32(a.w) * b.w);
+      }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) *reinterpret_cast<volatile int*>(P.counters + 2 * S.pairs_total + d.ctr) = 1;  // h chunk complete
+      continue;
+    }
+    if (P.S <= 2) {
+      // Down projections of at most two slots: the slot sets of both (28 bits each, one bit per
+      // quantum) ride above an 8-bit arrival count in one 64-bit word per column chunk.
+      __threadfence();
+      __syncwarp();
+      unsigned cnt = 0, m0 = 0, m1 = 0;
+      if (lane == 0) {
+        unsigned long long* c64 = reinterpret_cast<unsigned long long*>(P.counters) + ((3 * S.pairs_total + 1) >> 1) + d.c;
+        const unsigned long long mine = 1ull << (8 + 28 * d.s + d.qa);
+        const unsigned long long old = atomicAdd(c64, static_cast<unsigned long long>(d.qb - d.qa) | mine);
+        cnt = static_cast<unsigned>(old & 0xffu) + static_cast<unsigned>(d.qb - d.qa);
+        const unsigned long long m = (old | mine) >> 8;
+        m0 = static_cast<unsigned>(m) & 0xfffffffu;
+        m1 = static_cast<unsigned>(m >> 28) & 0xfffffffu;
+        if (static_cast<int>(cnt) == d.expected) *c64 = 0ull;
+      }
+      cnt = __shfl_sync(0xffffffffu, cnt, 0);
+      m0 = __shfl_sync(0xffffffffu, m0, 0);
+      m1 = __shfl_sync(0xffffffffu, m1, 0);
+      if (static_cast<int>(cnt) != d.expected) continue;
+      __threadfence();
+      if (col_on) {
+        float4 x2[2];
+        drain_pair(P.partial + S.slot[0].colb[1] + n, P.partial + S.slot[P.S - 1].colb[1] + n, ct, m0, P.S > 1 ? m1 : 0u,
+                   x2[0], x2[1]);
+        float4 accw = make_float4(0.f, 0.f, 0.f, 0.f), res = accw;
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+          if (s < P.S) {
+            const float4 v = round_half4(x2[s]);
+            if (s < P.A) {
+              const float wgt = __half2float(S.sel_w[s]);
+              accw.x = fmaf(wgt, v.x, accw.x); accw.y = fmaf(wgt, v.y, accw.y);
+              accw.z = fmaf(wgt, v.z, accw.z); accw.w = fmaf(wgt, v.w, accw.w);
+              if (s == P.A - 1) res = round_half4(accw);
+            } else {
+              res = round_half4(make_float4(res.x + v.x, res.y + v.y, res.z + v.z, res.w + v.w));
+            }
+          }
+        store_half4(P.out + n, res);
+      }
+      continue;
+    }
+    if (lane == 0) atomicOr(cw + d.mask, 1u << (d.qa & 31));
+    __threadfence();
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      const int add = d.qb - d.qa;
+      const int old = atomicAdd(P.counters + d.ctr, add);
+      last = (old + add == d.expected);
+      if (last) P.counters[d.ctr] = 0;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) continue;
+    __threadfence();
+    {
+      if (col_on) {
+        float4 accw = make_float4(0.f, 0.f, 0.f, 0.f), res = accw;
+        for (int s = 0; s < P.S; ++s) {
+          const SlotInfo& I = S.slot[s];
+          const float4 x2 = round_half4(drain_slots(P.partial + I.colb[1] + n, ct, cw + I.maskb[1] + d.c, I.nq[1]));
+          if (s < P.A) {
+            const float wgt = __half2float(S.sel_w[s]);
+            accw.x = fmaf(wgt, x2.x, accw.x); accw.y = fmaf(wgt, x2.y, accw.y);
+            accw.z = fmaf(wgt, x2.z, accw.z); accw.w = fmaf(wgt, x2.w, accw.w);
+            if (s == P.A - 1) res = round_half4(accw);
+          } else {
+            res = round_half4(make_float4(res.x + x2.x, res.y + x2.y, res.z + x2.z, res.w + x2.w));
+          }
+        }
+        store_half4(P.out + n, res);
+      }
+      __syncwarp();
+      if (lane == 0)
+        for (int s = 0; s < P.S; ++s) cw[S.slot[s].maskb[1] + d.c] = 0u;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_constant__ FusedParams P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  Smem& S = *reinterpret_cast<Smem*>(smem_raw);
+  __shared__ __align__(16) uint32_t zero_row[16];
+  const int warp = threadIdx.x >> 5;
+  int* err = P.counters + kErrSlot;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRedSlots; ++s) {
+      mbar_init(&S.redfull[s], kCons);
+      mbar_init(&S.redempty[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < 16) zero_row[threadIdx.x] = 0u;
+  // Ahead of the dependency wait: what does not depend on earlier kernels.  The per-expert bit
+  // widths and offsets go to shared memory, the router matrix is pulled into L2.
+  if (P.E <= kMetaE) {
+    for (int i = threadIdx.x; i < 7 * P.E; i += kThreads) {
+      const int a = i / P.E, e = i - a * P.E;
+      const int* src = a == 0 ? P.nbits1 : a == 1 ? P.nbits2 : a == 2 ? P.wqs1 : a == 3 ? P.wqs2
+                     : a == 4 ? P.zss1 : a == 5 ? P.zss3 : P.zss2;
+      S.emeta[a][e] = src ? src[e] : 0;
+    }
+  }
+  if (P.do_route) {
+    const size_t lines = (static_cast<size_t>(P.E) * P.D * sizeof(__half) + 127) / 128;
+    for (size_t i = threadIdx.x; i < lines; i += kThreads)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(P.gate) + i * 128));
+  }
+  // The next kernel of the stream may start its prologue; everything below reads results of
+  // the previous kernel (the activation, the zeroed workspace) and therefore waits for it.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (P.do_route) {
+    route_cta(S, P);
+  } else if (threadIdx.x < P.A) {
+    S.sel_e[threadIdx.x] = static_cast<int>(P.idx[threadIdx.x]);
+    S.sel_w[threadIdx.x] = P.w[threadIdx.x];
+  }
+  __syncthreads();
+  if (warp == 0) make_plan(S, P);
+  __syncthreads();
+  if (S.overflow && threadIdx.x == 0) atomicExch(err, 14);
+  __syncthreads();
+  if (warp < kCons) consumer_role(S, P, zero_row, err);
+  else finisher_role(S, P, err);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int old = atomicAdd(P.counters + kExitSlot, 1);
+    S.overflow = old == static_cast<int>(gridDim.x) - 1;  // the last CTA: nobody reads the h flags any more
+  }
+  __syncthreads();
+  if (S.overflow) {
+    for (int i = threadIdx.x; i < S.pairs_total; i += kThreads) P.counters[2 * S.pairs_total + i] = 0;
+    if (threadIdx.x == 0) P.counters[kExitSlot] = 0;
+  }
+}
+
+}  // namespace fused
+
+// ---- host ----------------------------------------------------------------------------------------
+static int fused_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static fused::Mat3 mat_of(const gemq_stacked_t& W) {
+  return {reinterpret_cast<const uint32_t*>(W.wq), static_cast<const __half*>(W.scales), static_cast<const __half*>(W.zeros)};
+}
+static fused::Mat3 mat_of(const gemq_single_t& W) {
+  return {reinterpret_cast<const uint32_t*>(W.wq), static_cast<const __half*>(W.scales), static_cast<const __half*>(W.zeros)};
+}
+static bool mat_aligned(const fused::Mat3& m) { return aligned16(m.wq) && aligned16(m.sc) && aligned16(m.zr); }
+
+// True when the fused kernel takes this layer; the limits are the table sizes (reduction
+// lengths up to kMaxK), the counter words and the per-CTA part list.
+bool decode_fused_ok(const gemq_moe_layer_t* L, size_t partial_floats) {
+  using namespace fused;
+  const int D = L->hidden, F = L->ffn, A = L->top_k, SF = L->shared_ffn;
+  if (L->group_size != kGroup || D % 128 || F % 128 || SF % 128) return false;
+  if (D > kMaxK || F > kMaxK || SF > kMaxK || A > kMaxSlots) return false;
+  if (D > 8192) return false;  // the slot set of a gate / up chunk (one bit per quantum) must fit 16 bits
+  if (SF > 0 && (L->s1.group_size != kGroup || L->s3.group_size != kGroup || L->s2.group_size != kGroup)) return false;
+  if (!mat_aligned(mat_of(L->w1)) || !mat_aligned(mat_of(L->w3)) || !mat_aligned(mat_of(L->w2))) return false;
+  if (SF > 0 && (!mat_aligned(mat_of(L->s1)) || !mat_aligned(mat_of(L->s3)) || !mat_aligned(mat_of(L->s2)))) return false;
+  const int S = A + (SF > 0 ? 1 : 0);
+  const int pairs = A * (F / 128) + SF / 128, nch1 = D / 128;
+  if (3 * pairs + (S + 1) * nch1 + 8 >= kMaxCounters) return false;
+  const int maxf = F > SF ? F : SF;
+  const size_t c_total = static_cast<size_t>(2 * (A * F + SF) > S * D ? 2 * (A * F + SF) : S * D);
+  const size_t slices = static_cast<size_t>(cdiv(cdiv(D > maxf ? D : maxf, kGroup), 4));
+  if (slices * c_total > partial_floats) return false;
+  // parts per CTA (a part is a run of quanta of one matrix and column chunk): bound for any bit widths
+  int sms = fused_sm_count();
+  if (sms <= 0) return false;
+  const int u0 = pairs * 2 * cdiv(D / kGroup, 4), u1 = nch1 * (A * cdiv(F / kGroup, 4) + cdiv(SF / kGroup, 4));
+  const int grid = (u0 > u1 ? u0 : u1) < sms ? (u0 > u1 ? u0 : u1) : sms;
+  const int nq0 = cdiv(D / kGroup, 5), nq1 = cdiv((SF > 0 && SF < F ? SF : F) / kGroup, 5);
+  const int parts = cdiv(cdiv(u0, grid) + S, nq0) + cdiv(cdiv(u1, grid) + S, nq1) + 4 * S + 4;
+  return parts <= kMaxParts;
+}
+
+// Launch the fused layer kernel for one token.  `route_in_kernel`: the router runs inside the
+// launch (E <= 32, D % 256 == 0); otherwise idx / w hold the routing already.
+int launch_decode_fused(const gemq_moe_layer_t* L, const __half* x, __half* out, int64_t* idx, __half* w,
+                        int route_in_kernel, int route_mode, float* partial, int* counters, float* h,
+                        cudaStream_t stream) {
+  using namespace fused;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const size_t smem = sizeof(Smem);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return GEMQ_ERR_LAUNCH;
+    attr_set[dev] = true;
+  }
+  const int sms = fused_sm_count();
+  if (sms <= 0) return GEMQ_ERR_LAUNCH;
+  FusedParams P = {};
+  P.x = x; P.gate = static_cast<const __half*>(L->gate); P.out = out;
+  P.idx = reinterpret_cast<long long*>(idx); P.w = w;
+  P.D = L->hidden; P.F = L->ffn; P.E = L->n_experts; P.A = L->top_k; P.SF = L->shared_ffn;
+  P.S = P.A + (P.SF > 0 ? 1 : 0);
+  P.do_route = route_in_kernel; P.route_mode = route_mode; P.renorm = L->renorm;
+  P.w1 = mat_of(L->w1); P.w3 = mat_of(L->w3); P.w2 = mat_of(L->w2);
+  P.nbits1 = L->w1.nbits; P.wqs1 = L->w1.wq_strides; P.zss1 = L->w1.zs_strides; P.zss3 = L->w3.zs_strides;
+  P.nbits2 = L->w2.nbits; P.wqs2 = L->w2.wq_strides; P.zss2 = L->w2.zs_strides;
+  if (P.SF > 0) {
+    P.s1 = mat_of(L->s1); P.s3 = mat_of(L->s3); P.s2 = mat_of(L->s2);
+    P.sbits = L->s1.nbits;
+  }
+  P.partial = partial; P.counters = counters; P.h = h;
+  const int up_cols = 2 * (P.A * P.F + P.SF), down_cols = P.S * P.D;
+  P.c_total = up_cols > down_cols ? up_cols : down_cols;
+  // at least one quantum per CTA in the larger phase (a quantum is at most 5 groups)
+  const int u0 = (P.A * (P.F / 128) + P.SF / 128) * 2 * cdiv(P.D / kGroup, 5);
+  const int u1 = (P.D / 128) * (P.A * cdiv(P.F / kGroup, 5) + (P.SF > 0 ? cdiv(P.SF / kGroup, 5) : 0));
+  const int units = u0 > u1 ? u0 : u1;
+  const int grid = units < sms ? (units < 1 ? 1 : units) : sms;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, moe_decode_kernel, P) != cudaSuccess) return GEMQ_ERR_LAUNCH;
+  return launch_status();
+}
+
+}  // namespace gemq
+

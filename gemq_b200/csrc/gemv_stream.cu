@@ -1060,7 +1060,7 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
     P.jobs[i].mask_base = words;
     words += cdiv(P.jobs[i].N, 128);
   }
-  if (words >= kErrSlot) return GEMQ_ERR_WORKSPACE;
+  if (words >= kErrSlot - 2) return GEMQ_ERR_WORKSPACE;  // the two words below it belong to the single-launch layer kernel
   if (static_cast<size_t>(max_slices) * cols > partial_floats) return GEMQ_ERR_WORKSPACE;
   P.c_total = cols;
   P.n_chunks = chunks;

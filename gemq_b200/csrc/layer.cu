@@ -1,6 +1,8 @@
 // One-token forward of a quantised MoE layer: router, fused gate/up projection,
 // SiLU*mul + down projection with the top-k combine folded into its epilogue.
 // Three launches, no host involvement between them.
+#include <cstdlib>
+
 #include "gemv.cuh"
 
 namespace gemq {
@@ -57,6 +59,22 @@ static void single_job(GemvJob& J, const gemq_single_t& W, int N, int K) {
   J.K = K;
 }
 
+// decode_fused.cu
+bool decode_fused_ok(const gemq_moe_layer_t* L, size_t partial_floats);
+int launch_decode_fused(const gemq_moe_layer_t* L, const __half* x, __half* out, int64_t* idx, __half* w,
+                        int route_in_kernel, int route_mode, float* partial, int* counters, float* h,
+                        cudaStream_t stream);
+
+// GEMQ_B200_DECODE=stream selects the three-launch path (router, gate/up GEMV, down GEMV) for
+// layers the single-launch kernel would take; read once.
+static bool fused_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("GEMQ_B200_DECODE");
+    return !(v && v[0] == 's');
+  }();
+  return on;
+}
+
 }  // namespace gemq
 
 using namespace gemq;
@@ -79,6 +97,30 @@ extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* o
   DecodeScratch S;
   if (!carve(L, scratch, scratch_bytes, &S)) return GEMQ_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  // Single-launch path: router, both projections and the combine in one persistent kernel per token.
+  {
+    int* counters = static_cast<int*>(S.gemv_ws);
+    float* partial = reinterpret_cast<float*>(static_cast<char*>(S.gemv_ws) + kMaxCounters * sizeof(int));
+    const size_t partial_floats = (S.gemv_ws_bytes - kMaxCounters * sizeof(int)) / sizeof(float);
+    if (fused_enabled() && aligned16(x) && aligned16(out) && aligned16(L->gate) && decode_fused_ok(L, partial_floats)) {
+      const bool in_kernel = do_route && L->n_experts <= 32 && A <= L->n_experts && D % 256 == 0;
+      if (do_route && !in_kernel) {
+        const int rc = gemq_moe_route(x, L->gate, tokens, D, L->n_experts, A, route_mode, L->renorm, 0, idx, w, nullptr,
+                                      stream);
+        if (rc) return rc;
+      }
+      for (int t = 0; t < tokens; ++t) {
+        const int rc = launch_decode_fused(L, static_cast<const __half*>(x) + static_cast<size_t>(t) * D,
+                                           static_cast<__half*>(out) + static_cast<size_t>(t) * D,
+                                           idx + static_cast<size_t>(t) * A,
+                                           static_cast<__half*>(w) + static_cast<size_t>(t) * A, in_kernel ? 1 : 0,
+                                           route_mode, partial, counters, S.h, st);
+        if (rc) return rc;
+      }
+      return GEMQ_OK;
+    }
+  }
 
   if (do_route) {
     const int rc = gemq_moe_route(x, L->gate, tokens, D, L->n_experts, A, route_mode, L->renorm, 0, idx, w, nullptr,
