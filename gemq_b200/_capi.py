@@ -29,7 +29,7 @@ class GemqError(RuntimeError):
 class Stacked(C.Structure):
     _fields_ = [("wq", C.c_void_p), ("scales", C.c_void_p), ("zeros", C.c_void_p),
                 ("nbits", C.c_void_p), ("wq_strides", C.c_void_p), ("zs_strides", C.c_void_p),
-                ("wq_rows", C.c_int64), ("zs_rows", C.c_int64)]
+                ("wq_rows", C.c_int64), ("zs_rows", C.c_int64), ("n_experts", C.c_int32)]
 
 
 class Single(C.Structure):
@@ -66,6 +66,8 @@ _SIGNATURES = {
     "gemq_moe_prefill_error_word": (_P, [C.POINTER(MoeLayer), _I, _P]),
     "gemq_dequant_gemv_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "gemq_static_scratch_bytes": (_Z, []),
+    "gemq_workspace_error_word": (_P, [_P]),
+    "gemq_workspace_wait_limit_word": (_P, [_P]),
     "gemq_moe_decode": (_I, [C.POINTER(MoeLayer), _P, _P, _P, _P, _I, _I, _I, _P, _Z, _P]),
 }
 
@@ -91,7 +93,8 @@ lib = _load()
 def stacked(wq, scales, zeros, nbits, wq_strides, zs_strides=None) -> Stacked:
     """Describe stacked-expert torch tensors for the library (borrowed pointers)."""
     return Stacked(wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(), nbits.data_ptr(), wq_strides.data_ptr(),
-                   zs_strides.data_ptr() if zs_strides is not None else None, wq.shape[0], scales.shape[0])
+                   zs_strides.data_ptr() if zs_strides is not None else None, wq.shape[0], scales.shape[0],
+                   int(nbits.numel()))
 
 
 def check(fn: str, code: int) -> None:

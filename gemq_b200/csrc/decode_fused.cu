@@ -56,7 +56,7 @@ constexpr int kMaxGroups = kMaxK / kGroup;
 constexpr int kMaxParts = 40;
 constexpr int kRouteMaxE = 32;
 constexpr int kMetaE = 64;
-constexpr int kErrSlot = kMaxCounters - 1;   // same word as the other decode kernels
+constexpr int kErrSlot = kErrWord;
 constexpr int kExitSlot = kMaxCounters - 3;  // CTAs that left this launch
 // words of activation tables: three digit planes of kMaxK bytes (+ padding), or the 3-bit
 // tables (16 halves per packed row + 16 per group for the rows that straddle two groups)
@@ -64,7 +64,7 @@ constexpr int kTabWordsI8 = 3 * (kMaxK / 4 + 16);
 constexpr int kTabWordsB3 = ((kMaxK + 9) / 10) * 8 + 8 + kMaxGroups * 8;
 constexpr int kTabWords = kTabWordsI8 > kTabWordsB3 ? kTabWordsI8 : kTabWordsB3;
 
-enum { kErrRedFull = 11, kErrRedEmpty = 12, kErrPhase = 13 };
+enum { kErrBadExpert = 7, kErrRedFull = 11, kErrRedEmpty = 12, kErrPhase = 13 };
 
 
 struct Mat3 {
@@ -89,7 +89,8 @@ struct FusedParams {
   float* partial;        // [slices][c_total], zero between launches
   int* counters;         // zero between launches
   float* h;              // [A*F + SF]
-  int c_total;
+  int c_total;           // columns of a partial row: gate/up columns of all slots, then the down columns
+  int up_cols;
 };
 
 struct SlotInfo {
@@ -133,6 +134,7 @@ struct Smem {
   SlotInfo slot[kMaxS];
   PartDesc parts[kMaxParts];
   int n_parts, n_parts0, expected1, pairs_total, overflow;
+  int spin;  // polls a bounded wait may take
   int sel_e[kMaxS];
   __half sel_w[kMaxS];
   float logit[kRouteMaxE];
@@ -208,13 +210,13 @@ __device__ __forceinline__ uint32_t digits_word(float x, float f) { return __flo
 
 // Wait until the h chunks (= reduction groups of phase 1) [g0, g1) of a slot are complete.  Lane 0
 // polls; the flags are written by the finisher that completed the chunk, after a fence.
-__device__ __forceinline__ void wait_groups(const int* flags, int g0, int g1, int* err) {
+__device__ __forceinline__ void wait_groups(const int* flags, int g0, int g1, int* err, int spin) {
   if (flags) {
     if ((threadIdx.x & 31) == 0) {
       for (int gq = g0; gq < g1; ++gq) {
         int i = 0;
         while (ld_acquire(flags + gq) == 0) {
-          if (++i > kSpinLimit) { atomicExch(err, kErrPhase); break; }
+          if (++i > spin) { atomicExch(err, kErrPhase); break; }
           __nanosleep(32);
         }
       }
@@ -227,7 +229,7 @@ __device__ __forceinline__ void wait_groups(const int* flags, int g0, int g1, in
 // wanted 32-row blocks round robin.  A group is 4*B consecutive rows (= lanes).
 template <int B>
 __device__ __forceinline__ void build_i8(Tables& T, const void* x, bool xf32, int K, unsigned need, const int* flags,
-                                         int* err, int warp, int lane) {
+                                         int* err, int spin, int warp, int lane) {
   using F = I8<B>;
   constexpr int EPS = F::kEps, CPB = F::kCpb, LPG = 4 * B;
   const int rows = K / EPS;
@@ -237,7 +239,7 @@ __device__ __forceinline__ void build_i8(Tables& T, const void* x, bool xf32, in
     const int q0 = (row0 / LPG) >> 2, q1 = ((row0 + 31) / LPG) >> 2;
     if (q0 < 32 && !((need >> q0) & 1u) && !((need >> (q1 < 32 ? q1 : 31)) & 1u)) continue;
     if ((taken++ % kCons) != warp) continue;
-    wait_groups(flags, row0 / LPG, min(rows, row0 + 32) / LPG, err);
+    wait_groups(flags, row0 / LPG, min(rows, row0 + 32) / LPG, err, spin);
     const int row = row0 + lane;
     const bool on = row < rows;
     float xv[EPS];
@@ -317,7 +319,7 @@ __device__ __forceinline__ void build_i8(Tables& T, const void* x, bool xf32, in
 // A warp takes up to four groups at a time so that their loads are in flight together.
 __device__ __forceinline__ int b3_rows(int K) { return (K + 9) / 10; }
 __device__ __forceinline__ void build_b3(Tables& T, const void* x, bool xf32, int K, unsigned need, const int* flags,
-                                         int* err, int warp, int lane) {
+                                         int* err, int spin, int warp, int lane) {
   const int rows = b3_rows(K), ngroups = K / kGroup;
   uint32_t* tab1w = T.tab + rows * 8;
   const int words = rows * 8 + ngroups * 8;
@@ -337,7 +339,7 @@ __device__ __forceinline__ void build_b3(Tables& T, const void* x, bool xf32, in
 #pragma unroll
     for (int u = 0; u < 4; ++u)
       if (u < nmine) {
-        wait_groups(flags, mine[u], mine[u] + 1, err);
+        wait_groups(flags, mine[u], mine[u] + 1, err, spin);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const size_t k = static_cast<size_t>(mine[u]) * kGroup + i * 32 + lane;
@@ -380,12 +382,12 @@ __device__ __forceinline__ void build_b3(Tables& T, const void* x, bool xf32, in
 // word per group that turns non-zero when the group's slice of the vector exists (h in phase 1),
 // or nullptr.
 __device__ __noinline__ void build_table(Tables* T, const void* x, int xf32, int K, int B, unsigned need, const int* flags,
-                                         int* err, int warp, int lane) {
+                                         int* err, int spin, int warp, int lane) {
   bar_consumers();
-  if (B == 1) build_i8<1>(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
-  else if (B == 2) build_i8<2>(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
-  else if (B == 3) build_b3(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
-  else build_i8<4>(*T, x, xf32 != 0, K, need, flags, err, warp, lane);
+  if (B == 1) build_i8<1>(*T, x, xf32 != 0, K, need, flags, err, spin, warp, lane);
+  else if (B == 2) build_i8<2>(*T, x, xf32 != 0, K, need, flags, err, spin, warp, lane);
+  else if (B == 3) build_b3(*T, x, xf32 != 0, K, need, flags, err, spin, warp, lane);
+  else build_i8<4>(*T, x, xf32 != 0, K, need, flags, err, spin, warp, lane);
   bar_consumers();
 }
 
@@ -488,7 +490,10 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
     SlotInfo I;
     if (lane < P.A) {
       int e = S.sel_e[lane];
-      e = e < 0 ? 0 : (e >= P.E ? P.E - 1 : e);
+      if (e < 0 || e >= P.E) {  // caller-supplied routing with an id out of range: never index with it
+        atomicExch(P.counters + kErrSlot, kErrBadExpert);
+        e = e < 0 ? 0 : P.E - 1;
+      }
       const bool pre = P.E <= kMetaE;  // tables staged in shared memory ahead of the dependency wait
       b1 = clamp_bits(pre ? S.emeta[0][e] : P.nbits1[e]);
       b2 = clamp_bits(pre ? S.emeta[1][e] : P.nbits2[e]);
@@ -540,7 +545,7 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
     I.hoff = in_fs - fs;
     I.ctrb = in_nch - nch0;
     I.colb[0] = 2 * (in_fs - fs);
-    I.colb[1] = lane * P.D;
+    I.colb[1] = P.up_cols + lane * P.D;  // the phases overlap in time: their partial columns must not
     I.maskb[0] = pairs_total + 2 * (in_nch - nch0);
     I.maskb[1] = base1 + nch1 + lane * nch1;
   }
@@ -1024,7 +1029,7 @@ __device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zer
       }
       // the h chunks of a slot are the reduction groups of its down projection: their flags gate the build
       const int* flags = d.phase ? P.counters + 2 * S.pairs_total + S.slot[d.s].ctrb : nullptr;
-      build_table(&S.T, xsrc, d.phase, d.ngroups * kGroup, B, need, flags, err, warp, lane);
+      build_table(&S.T, xsrc, d.phase, d.ngroups * kGroup, B, need, flags, err, S.spin, warp, lane);
       cur_tab = d.tab;
     }
     if (B == 1) part_i8<1>(R, L, C, S, d, kq, lane);
@@ -1042,7 +1047,7 @@ __device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zer
           R.vs[j][s][e] += __shfl_xor_sync(0xffffffffu, R.vs[j][s][e], 2);
         }
     const int rs = p % kRedSlots;
-    mbar_wait(&S.redempty[rs], ((p / kRedSlots) & 1) ^ 1, err, kErrRedEmpty);
+    mbar_wait(&S.redempty[rs], ((p / kRedSlots) & 1) ^ 1, err, kErrRedEmpty, 64, S.spin);
     if (c == 0) {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
@@ -1149,7 +1154,7 @@ __device__ void finisher_role(Smem& S, const FusedParams& P, int* err) {
   const int rs = (threadIdx.x >> 5) - kCons;
   for (int p = rs; p < n_parts; p += kFin) {
     const PartDesc& d = S.parts[p];
-    mbar_wait(&S.redfull[rs], (p / kRedSlots) & 1, err, kErrRedFull);
+    mbar_wait(&S.redfull[rs], (p / kRedSlots) & 1, err, kErrRedFull, 64, S.spin);
     float4 r = *reinterpret_cast<const float4*>(&S.red[rs][0][4 * lane]);
 #pragma unroll
     for (int q = 1; q < kLanes; ++q) {
@@ -1309,6 +1314,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_co
   // the previous kernel (the activation, the zeroed workspace) and therefore waits for it.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) {
+    const int lim = P.counters[kLimitWord];
+    S.spin = lim > 0 ? lim : kSpinLimit;
+  }
   if (P.do_route) {
     route_cta(S, P);
   } else if (threadIdx.x < P.A) {
@@ -1373,7 +1382,7 @@ bool decode_fused_ok(const gemq_moe_layer_t* L, size_t partial_floats) {
   const int pairs = A * (F / 128) + SF / 128, nch1 = D / 128;
   if (3 * pairs + (S + 1) * nch1 + 8 >= kMaxCounters) return false;
   const int maxf = F > SF ? F : SF;
-  const size_t c_total = static_cast<size_t>(2 * (A * F + SF) > S * D ? 2 * (A * F + SF) : S * D);
+  const size_t c_total = static_cast<size_t>(2 * (A * F + SF) + S * D);
   const size_t slices = static_cast<size_t>(cdiv(cdiv(D > maxf ? D : maxf, kGroup), 4));
   if (slices * c_total > partial_floats) return false;
   // parts per CTA (a part is a run of quanta of one matrix and column chunk): bound for any bit widths
@@ -1419,7 +1428,8 @@ int launch_decode_fused(const gemq_moe_layer_t* L, const __half* x, __half* out,
   }
   P.partial = partial; P.counters = counters; P.h = h;
   const int up_cols = 2 * (P.A * P.F + P.SF), down_cols = P.S * P.D;
-  P.c_total = up_cols > down_cols ? up_cols : down_cols;
+  P.c_total = up_cols + down_cols;
+  P.up_cols = up_cols;
   // at least one quantum per CTA in the larger phase (a quantum is at most 5 groups)
   const int u0 = (P.A * (P.F / 128) + P.SF / 128) * 2 * cdiv(P.D / kGroup, 5);
   const int u1 = (P.D / 128) * (P.A * cdiv(P.F / kGroup, 5) + (P.SF > 0 ? cdiv(P.SF / kGroup, 5) : 0));

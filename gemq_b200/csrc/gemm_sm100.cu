@@ -38,18 +38,6 @@ constexpr int kTileBytes = kGemmBN * kGemmBK * 2;  // 16 KB: a B tile, or one 12
 
 enum { kErrGemmAFull = 11, kErrGemmBFull = 12, kErrGemmEmpty = 13, kErrGemmAcc = 14 };
 
-#ifdef GEMQ_GEMM_TRACE
-// Development aid: nanosecond stamps of one CTA's roles (compiled out of the product build).
-__device__ unsigned long long g_gtrace[8][80];
-__device__ __forceinline__ unsigned long long gemm_gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define GTRACE(row, i) do { if (blockIdx.x == 10 && blockIdx.y == 2 && (i) < 80) g_gtrace[row][i] = gemm_gtime(); } while (0)
-#else
-#define GTRACE(row, i) do { } while (0)
-#endif
 
 struct alignas(64) GemmParams {
   CUtensorMap a_map;        // activations [rows, K] (16-bit), box 64 x 256, 128B swizzle
@@ -229,7 +217,6 @@ __device__ __forceinline__ void produce_loop(GemmSmem& S, const GemmParams& P, i
   auto produce = [&](const WSet& W, int kb) {
     const int s = kb % kGemmStages;
     mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
-    if ((tid & 255) == 0) GTRACE(0, kb);
 #pragma unroll
     for (int m = 0; m < NMAT; ++m) {
       const __half2 s2 = __half2half2(W.sc[m]), z2 = __half2half2(W.zr[m]);
@@ -240,7 +227,6 @@ __device__ __forceinline__ void produce_loop(GemmSmem& S, const GemmParams& P, i
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor-core reads
     __syncwarp();
     if (lane == 0) mbar_arrive(&S.b_full[s]);
-    if ((tid & 255) == 0) GTRACE(1, kb);
   };
   if (grp < KB) fetch(ring[0], grp);
   if (grp + 2 < KB) fetch(ring[1], grp + 2);
@@ -380,7 +366,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         mbar_wait(&S.empty[s], ((kb / kGemmStages) & 1) ^ 1, P.err, kErrGemmEmpty, 32);
         mbar_arrive_expect_tx(&S.a_full[s], 2 * kTileBytes);
         tma_load_2d(S.a[s], &P.a_map, kb * kGemmBK, row0, &S.a_full[s]);
-        GTRACE(2, kb);
       }
     }
   } else {
@@ -394,9 +379,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         const int s = kb % kGemmStages;
         const uint32_t par = (kb / kGemmStages) & 1;
         mbar_wait(&S.a_full[s], par, P.err, kErrGemmAFull, 32);
-        GTRACE(3, kb);
         mbar_wait(&S.b_full[s], par, P.err, kErrGemmBFull, 32);
-        GTRACE(4, kb);
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(S.a[s]);
 #pragma unroll
@@ -407,7 +390,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                      (kb | k4) != 0);
         }
         umma_commit(&S.empty[s]);  // stage is free once these MMAs have read it
-        GTRACE(5, kb);
       }
       umma_commit(&S.acc_full);
     }
@@ -443,9 +425,16 @@ __global__ void prefill_zero_kernel(PrefillPlan pl, int E) {
   if (i < E) { pl.counts[i] = 0; pl.cursor[i] = 0; }
 }
 
-__global__ void prefill_count_kernel(PrefillPlan pl, const long long* __restrict__ idx, int n) {
+// Expert ids outside [0, E) (only possible with caller-supplied routing) are left out of the
+// permutation and reported through the error word; they contribute nothing to the output.
+constexpr int kErrBadExpert = 21;
+
+__global__ void prefill_count_kernel(PrefillPlan pl, const long long* __restrict__ idx, int n, int E, int* err) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) atomicAdd(&pl.counts[static_cast<int>(idx[i])], 1);
+  if (i >= n) return;
+  const long long e = idx[i];
+  if (e < 0 || e >= E) { atomicExch(err, kErrBadExpert); return; }
+  atomicAdd(&pl.counts[static_cast<int>(e)], 1);
 }
 
 // One thread: exclusive scan of the expert counts and the row-tile table (E <= 256).
@@ -493,18 +482,21 @@ __device__ __forceinline__ uint4 to_half8(uint4 v) {
 template <typename T>
 __global__ void prefill_scatter_kernel(PrefillPlan pl, const long long* __restrict__ idx, const T* __restrict__ w,
                                        const T* __restrict__ x, __half* __restrict__ xs, __half* __restrict__ row_w,
-                                       int n, int A, int D) {
+                                       int n, int A, int D, int E) {
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (i >= n) return;
-  int pos = 0;
+  int pos = -1;
   if (lane == 0) {
-    const int e = static_cast<int>(idx[i]);
-    pos = pl.offsets[e] + atomicAdd(&pl.cursor[e], 1);
+    const long long e = idx[i];
+    if (e >= 0 && e < E) {
+      pos = pl.offsets[e] + atomicAdd(&pl.cursor[e], 1);
+      row_w[pos] = __float2half_rn(ActT<T>::f(w[i]));
+    }
     pl.inv[i] = pos;
-    row_w[pos] = __float2half_rn(ActT<T>::f(w[i]));
   }
   pos = __shfl_sync(0xffffffffu, pos, 0);
+  if (pos < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(i / A) * D);
   uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(pos) * D);
   for (int k = lane; k < D / 8; k += 32) dst[k] = to_half8<T>(src[k]);
@@ -534,6 +526,7 @@ __global__ void prefill_combine_kernel(const int* __restrict__ inv, const long l
     float acc = 0.f;
     for (int a = 0; a < A; ++a) {
       const int row = inv[t * A + order[a]];
+      if (row < 0) continue;  // pair with an expert id out of range
       const float c = ActT<T>::f(ActT<T>::r(__half2float(ys[static_cast<size_t>(row) * D + d])));
       acc = ActT<T>::f(ActT<T>::r(acc + c));
     }
@@ -696,16 +689,16 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
   }
   prefill_zero_kernel<<<cdiv(E + 2, 256), 256, 0, st>>>(S.plan, E);
   cudaMemsetAsync(S.err, 0, sizeof(int), st);
-  prefill_count_kernel<<<cdiv(R, 256), 256, 0, st>>>(S.plan, reinterpret_cast<const long long*>(idx), R);
+  prefill_count_kernel<<<cdiv(R, 256), 256, 0, st>>>(S.plan, reinterpret_cast<const long long*>(idx), R, E, S.err);
   prefill_plan_kernel<<<1, 32, 0, st>>>(S.plan, E, S.max_tiles);
   if (bf)
     prefill_scatter_kernel<__nv_bfloat16><<<cdiv(R, 8), 256, 0, st>>>(
         S.plan, reinterpret_cast<const long long*>(idx), static_cast<const __nv_bfloat16*>(w),
-        static_cast<const __nv_bfloat16*>(x), static_cast<__half*>(S.xs), static_cast<__half*>(S.row_w), R, A, D);
+        static_cast<const __nv_bfloat16*>(x), static_cast<__half*>(S.xs), static_cast<__half*>(S.row_w), R, A, D, E);
   else
     prefill_scatter_kernel<__half><<<cdiv(R, 8), 256, 0, st>>>(
         S.plan, reinterpret_cast<const long long*>(idx), static_cast<const __half*>(w), static_cast<const __half*>(x),
-        static_cast<__half*>(S.xs), static_cast<__half*>(S.row_w), R, A, D);
+        static_cast<__half*>(S.xs), static_cast<__half*>(S.row_w), R, A, D, E);
   if (int rc = launch_status()) return rc;
 
   // gate/up GEMMs with the SiLU*mul epilogue
@@ -781,8 +774,3 @@ extern "C" const int32_t* gemq_moe_prefill_error_word(const gemq_moe_layer_t* L,
   return S.err;
 }
 
-#ifdef GEMQ_GEMM_TRACE
-extern "C" int gemq_debug_read_gemm_trace(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, gemq::g_gtrace, sizeof(gemq::g_gtrace)) == cudaSuccess ? 0 : -1;
-}
-#endif

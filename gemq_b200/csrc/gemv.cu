@@ -731,6 +731,7 @@ static void job_from_stacked(GemvJob& J, const gemq_stacked_t* W, const int64_t*
   J.zs_rows = W->zs_rows;
   J.N = N;
   J.K = K;
+  J.n_experts = W->n_experts;
 }
 
 static bool stacked_ok(const gemq_stacked_t* W) {

@@ -22,6 +22,8 @@ constexpr int kSliceGroups = 8;           // k-slice of a CTA: 8 groups (1/2/4-b
 constexpr int kSliceGroupsB3 = 10;        //                   10 groups (3-bit: two 640-wide spans)
 constexpr int kRing = 8;                  // 128-bit weight loads in flight per lane
 constexpr int kMaxCounters = 8192;        // arrival counters at the head of the workspace
+constexpr int kErrWord = kMaxCounters - 1;   // error code of the decode kernels (0 = none)
+constexpr int kLimitWord = kMaxCounters - 4; // caller-set poll limit of the layer kernel's bounded waits (0 = built in)
 constexpr int kMaxFamilies = 4;           // distinct (wq, scales, zeros) tensor triples per launch
 constexpr int kMaxMaps = 3 * kMaxFamilies;
 
@@ -33,6 +35,7 @@ struct GemvJob {
   const int* wq_strides;   // [E] word offsets or nullptr -> 0
   const int* zs_strides;   // [E] element offsets or nullptr -> e * (K/G) * N
   const long long* idx;    // address of this job's expert id, nullptr -> expert 0
+  int n_experts;           // experts in the stacked tensors (0: unknown); ids are clamped into [0, n_experts)
   const __half* xa;        // activation rows [T, K]; with SILU: x1 of this slot
   const __half* xb;        // with SILU: x3 of this slot
   __half* y;               // output rows [T, N] (may be nullptr in combine mode)
@@ -92,7 +95,8 @@ __device__ __forceinline__ int slice_groups(int bits) { return bits == 3 ? kSlic
 
 __device__ __forceinline__ ResolvedJob resolve_job(const GemvJob& J, int G) {
   ResolvedJob R;
-  const int e = J.idx ? static_cast<int>(*J.idx) : 0;
+  int e = J.idx ? static_cast<int>(*J.idx) : 0;
+  if (J.n_experts > 0) e = e < 0 ? 0 : (e >= J.n_experts ? J.n_experts - 1 : e);
   R.bits = J.nbits ? J.nbits[e] : J.fixed_bits;
   const int ngroups = J.K / G;
   const size_t zoff = J.zs_strides ? static_cast<size_t>(J.zs_strides[e])

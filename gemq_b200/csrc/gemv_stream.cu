@@ -40,27 +40,10 @@ constexpr int kRedSlots = 4;
 constexpr int kUnitRows = 64;
 constexpr int kStripBytes = kUnitRows * 128;  // one TMA box: 64 word rows x 32 columns, 128B-swizzled
 constexpr int kMaxUnitGroups = 16;
-constexpr int kErrSlot = kMaxCounters - 1;  // last counter word holds the error code
+constexpr int kErrSlot = kErrWord;
 
-#ifdef GEMQ_STREAM_TRACE
-// Development aid: nanosecond stamps of one CTA's roles (compiled out of the product build).
-__device__ unsigned long long g_trace[10][256];
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define TRACE(row, i) do { if (!P.x_f32 && blockIdx.x == 70 && (threadIdx.x & 31) == 0 && (i) < 256) g_trace[row][i] = gtime(); } while (0)
-// per launch (ring of 64) and CTA: entry, dependencies resolved, roles start, end
-__device__ unsigned long long g_life[64][160][4];
-__device__ unsigned int g_life_id;
-#define LIFE(k) do { if (threadIdx.x == 0) g_life[life_id & 63][blockIdx.x][k] = gtime(); } while (0)
-#else
-#define LIFE(k) do { } while (0)
-#define TRACE(row, i) do { } while (0)
-#endif
 
-enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrRedFullWait = 3, kErrRedEmptyWait = 4, kErrTabFullWait = 5, kErrTabEmptyWait = 6 };
+enum { kErrBadExpert = 7, kErrFullWait = 1, kErrEmptyWait = 2, kErrRedFullWait = 3, kErrRedEmptyWait = 4, kErrTabFullWait = 5, kErrTabEmptyWait = 6 };
 
 struct StageBuf {
   alignas(1024) unsigned char words[4 * kStripBytes];
@@ -176,7 +159,7 @@ struct PlanArgs {
   const int* nbits;
   const int* wq_strides;
   const int* zs_strides;
-  int fixed_bits, N, K, map_base;
+  int fixed_bits, N, K, map_base, n_experts;
 };
 
 __device__ __forceinline__ void read_plan_args(const GemvParams& P, PlanArgs& A) {
@@ -184,7 +167,7 @@ __device__ __forceinline__ void read_plan_args(const GemvParams& P, PlanArgs& A)
   if (lane < P.n_jobs) {
     const GemvJob& J = P.jobs[lane];
     A.idx = J.idx; A.nbits = J.nbits; A.wq_strides = J.wq_strides; A.zs_strides = J.zs_strides;
-    A.fixed_bits = J.fixed_bits; A.N = J.N; A.K = J.K; A.map_base = J.map_base;
+    A.fixed_bits = J.fixed_bits; A.N = J.N; A.K = J.K; A.map_base = J.map_base; A.n_experts = J.n_experts;
   }
 }
 
@@ -194,7 +177,11 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P, const PlanArgs& J)
   const int lane = threadIdx.x & 31;
   unsigned n_units = 0, unit_cost = 1;
   if (lane < P.n_jobs) {
-    const int e = J.idx ? static_cast<int>(*J.idx) : 0;
+    int e = J.idx ? static_cast<int>(*J.idx) : 0;
+    if (J.n_experts > 0 && (e < 0 || e >= J.n_experts)) {  // never index the tables with a bad id
+      atomicExch(P.counters + kErrSlot, kErrBadExpert);
+      e = e < 0 ? 0 : J.n_experts - 1;
+    }
     const int bits = J.nbits ? J.nbits[e] : J.fixed_bits;
     JobInfo I;
     I.ngroups = J.K / kGroup;
@@ -248,24 +235,20 @@ __device__ void make_plan(StreamSmem& S, const GemvParams& P, const PlanArgs& J)
 // ---- producer ---------------------------------------------------------------------------
 __device__ void producer_role(StreamSmem& S, const GemvParams& P, int* err) {
   const int lane = threadIdx.x & 31;
-  TRACE(7, 5);
   PartWalk W;
   W.begin(S);
   Part Pt;
   int it = 0;
   while (W.next(S, Pt)) {
-    if (it == 0) TRACE(7, 6);
     const GemvJob& J = P.jobs[Pt.job];
     const JobInfo& I = S.info[Pt.job];
     for (int sl = Pt.sa; sl < Pt.sb; ++sl, ++it) {
       Unit U;
       make_unit(J, I, Pt.job, sl, Pt.chunk, U);
-      if (it == 0) TRACE(7, 7);
       const int st = it % kSStages;
       const uint32_t par = (it / kSStages) & 1;
       StageBuf& B = S.stage[st];
       mbar_wait(&S.empty[st], par ^ 1, err, kErrEmptyWait);
-      TRACE(0, it);
       const int nstrips = U.ncols / 32, nmeta = (U.ng + 3) / 4;
       if (lane == 0) mbar_arrive_expect_tx(&S.full[st], nstrips * kStripBytes + 2 * nmeta * 1024);
       __syncwarp();
@@ -277,7 +260,6 @@ __device__ void producer_role(StreamSmem& S, const GemvParams& P, int* err) {
         tma_load_2d(t ? static_cast<void*>(B.zeros[4 * q]) : static_cast<void*>(B.scales[4 * q]),
                     &P.maps[I.map_base + 1 + t], U.n0, I.zs_row0 + U.g0 + 4 * q, &S.full[st]);
       }
-      TRACE(1, it);
     }
   }
 }
@@ -462,7 +444,6 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw)
       make_unit(J, I, Pt.job, sl, Pt.chunk, U);
       const int ts = it % kTabSlots;
       mbar_wait(&S.tempty[ts], ((it / kTabSlots) & 1) ^ 1, err, kErrTabEmptyWait);
-      TRACE(2, it);
       TableBuf& T = S.table[ts];
       if (U.bits == 1) build_table_i8<1>(T, J.xa, U, XF32);
       else if (U.bits == 2) build_table_i8<2>(T, J.xa, U, XF32);
@@ -470,7 +451,6 @@ __device__ void table_role(StreamSmem& S, const GemvParams& P, int* err, int tw)
       else build_table_i8<4>(T, J.xa, U, XF32);
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.tfull[ts]);
-      TRACE(3, it);
     }
   }
 }
@@ -694,7 +674,6 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
       const TableBuf& T = S.table[ts];
       mbar_wait(&S.tfull[ts], (it / kTabSlots) & 1, err, kErrTabFullWait);
       mbar_wait(&S.full[st], (it / kSStages) & 1, err, kErrFullWait);
-      if (wl == 0) TRACE(4 + grp, it >> 1);
       if (strip_on && kRowsPerWarp * kp < nrows) {
         if (I.bits == 1) consume_i8<1>(B, T, S.zero_row, nrows, ng, cw, kp, vs);
         else if (I.bits == 2) consume_i8<2>(B, T, S.zero_row, nrows, ng, cw, kp, vs);
@@ -702,7 +681,6 @@ __device__ void consumer_role(StreamSmem& S, const GemvParams& P, int* err) {
         else consume_i8<4>(B, T, S.zero_row, nrows, ng, cw, kp, vs);
       }
       __syncwarp();
-      if (wl == 0) TRACE(8 + grp, it >> 1);
       if (lane == 0) {
         mbar_arrive(&S.empty[st]);
         mbar_arrive(&S.tempty[ts]);
@@ -835,7 +813,6 @@ __device__ void finisher_role(StreamSmem& S, const GemvParams& P, int* err) {
     const JobInfo& I = S.info[Pt.job];
     const int slot = pc % kRedSlots;
     mbar_wait(&S.redfull[slot], (pc / kRedSlots) & 1, err, kErrRedFullWait);
-    TRACE(6, pc);
     float4 r = *reinterpret_cast<const float4*>(&S.red[slot][0][4 * lane]);
 #pragma unroll
     for (int q = 1; q < 4; ++q) {
@@ -891,10 +868,6 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
   StreamSmem& S = *reinterpret_cast<StreamSmem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
-#ifdef GEMQ_STREAM_TRACE
-  const unsigned life_id = P.c_total == 0 ? 0u : static_cast<unsigned>(P.s_max >> 16);
-#endif
-  LIFE(0);
   int* err = P.counters + kErrSlot;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSStages; ++s) {
@@ -924,35 +897,14 @@ __global__ void __launch_bounds__(kSThreads, 1) gemv_stream_kernel(const __grid_
     if (P.plan_early) make_plan(S, P, plan_args);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  LIFE(1);
-  if (warp == 0) TRACE(7, 8);
-  if (warp == 1) TRACE(7, 11);
-  if (warp == 16) TRACE(7, 13);
   if (warp == 0 && !P.plan_early) make_plan(S, P, plan_args);
-#ifdef GEMQ_STREAM_TRACE
-  if (threadIdx.x == 0) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); g_life[life_id & 63][blockIdx.x][0] = smid; }
-#endif
-  if (warp == 0) TRACE(7, 9);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  if (warp == 0) TRACE(7, 10);
-  if (warp == 1) TRACE(7, 12);
-  if (warp == 1) TRACE(7, 0);
   __syncthreads();
-  if (warp == 1) TRACE(7, 1);
-  LIFE(2);
-#ifdef GEMQ_STREAM_TRACE
-  if (blockIdx.x == 70 && threadIdx.x == 32) g_trace[7][3] = clock64();
-#endif
   if (warp < kSConsumers) consumer_role(S, P, err);
   else if (warp == kWarpProducer) producer_role(S, P, err);
   else if (warp < kWarpFinisher) table_role(S, P, err, warp - kWarpTable);
   else finisher_role(S, P, err);
   __syncthreads();
-  if (warp == 1) TRACE(7, 2);
-  LIFE(3);
-#ifdef GEMQ_STREAM_TRACE
-  if (blockIdx.x == 70 && threadIdx.x == 32) g_trace[7][4] = clock64();
-#endif
 }
 
 // h[i] = silu(x1[i]) * x3[i] in fp32 (gemq/triton_kernels/fused_dequant_bmm.py:237-239)
@@ -1060,17 +1012,11 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
     P.jobs[i].mask_base = words;
     words += cdiv(P.jobs[i].N, 128);
   }
-  if (words >= kErrSlot - 2) return GEMQ_ERR_WORKSPACE;  // the two words below it belong to the single-launch layer kernel
+  if (words >= kMaxCounters - 4) return GEMQ_ERR_WORKSPACE;  // the last words are reserved (error code, wait limit, exit count)
   if (static_cast<size_t>(max_slices) * cols > partial_floats) return GEMQ_ERR_WORKSPACE;
   P.c_total = cols;
   P.n_chunks = chunks;
   P.s_max = max_slices;
-#ifdef GEMQ_STREAM_TRACE
-  {
-    static int launch_id = 0;
-    P.s_max |= (launch_id++ & 0x7fff) << 16;
-  }
-#endif
   P.G = kGroup;
   P.partial = partial;
   P.counters = counters;
@@ -1079,11 +1025,3 @@ int launch_stream(GemvParams& P, float* partial, size_t partial_floats, int* cou
 
 }  // namespace gemq
 
-#ifdef GEMQ_STREAM_TRACE
-extern "C" int gemq_debug_read_trace(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, gemq::g_trace, sizeof(gemq::g_trace)) == cudaSuccess ? 0 : -1;
-}
-extern "C" int gemq_debug_read_life(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, gemq::g_life, sizeof(gemq::g_life)) == cudaSuccess ? 0 : -1;
-}
-#endif

@@ -20,7 +20,8 @@ static size_t decode_ws_bytes(const gemq_moe_layer_t* L) {
   const int down_cols = (L->top_k + (L->shared_ffn > 0 ? 1 : 0)) * L->hidden;
   const int max_k = L->ffn > L->hidden ? L->ffn : L->hidden;
   const int mk = L->shared_ffn > max_k ? L->shared_ffn : max_k;
-  return align_up(gemv_workspace_bytes(up_cols > down_cols ? up_cols : down_cols, mk, 1), 256);
+  // the one-launch layer kernel keeps the partial sums of its two phases in disjoint columns
+  return align_up(gemv_workspace_bytes(up_cols + down_cols, mk, 1), 256);
 }
 
 static bool carve(const gemq_moe_layer_t* L, void* scratch, size_t bytes, DecodeScratch* S) {
@@ -46,6 +47,7 @@ static void stacked_job(GemvJob& J, const gemq_stacked_t& W, const int64_t* idx_
   J.zs_rows = W.zs_rows;
   J.N = N;
   J.K = K;
+  J.n_experts = W.n_experts;
 }
 
 static void single_job(GemvJob& J, const gemq_single_t& W, int N, int K) {
@@ -83,6 +85,14 @@ extern "C" size_t gemq_moe_decode_scratch_bytes(const gemq_moe_layer_t* L) {
   if (!L || L->hidden <= 0 || L->ffn <= 0 || L->top_k <= 0) return 0;
   const size_t act = align_up(static_cast<size_t>(L->top_k * L->ffn + L->shared_ffn) * sizeof(float), 256);
   return decode_ws_bytes(L) + act;
+}
+
+extern "C" int32_t* gemq_workspace_error_word(void* workspace) {
+  return workspace ? static_cast<int32_t*>(workspace) + kErrWord : nullptr;
+}
+
+extern "C" int32_t* gemq_workspace_wait_limit_word(void* workspace) {
+  return workspace ? static_cast<int32_t*>(workspace) + kLimitWord : nullptr;
 }
 
 extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* out,
@@ -179,7 +189,10 @@ extern "C" int gemq_moe_decode(const gemq_moe_layer_t* L, const void* x, void* o
     Q.n_jobs = nj;
     Q.epi = kEpiCombine;
     Q.x_f32 = 1;
-    Q.plan_early = 1;  // the ids were consumed by the up projection already; only h is new
+    // The down projection may resolve its experts ahead of its dependency wait only when the ids
+    // are older than the whole chain of launches of this call: supplied by the caller, or written
+    // by the router two or more launches back (rows after the first).
+    Q.plan_early = (!do_route || t > 0) ? 1 : 0;
     Q.comb_out = static_cast<__half*>(out) + static_cast<size_t>(t) * D;
     Q.comb_w = static_cast<const __half*>(w) + static_cast<size_t>(t) * A;
     Q.comb_weighted = A;

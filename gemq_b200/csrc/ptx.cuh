@@ -32,9 +32,9 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
 // Bounded wait: gives up after kSpinLimit polls, records `code` and returns.  A waiting warp
 // sleeps between polls so that it does not take issue slots from the warps that are working.
 __device__ __forceinline__ void mbar_wait(unsigned long long* bar, uint32_t parity, int* err, int code,
-                                          unsigned sleep_ns = 64) {
+                                          unsigned sleep_ns = 64, int limit = kSpinLimit) {
   if (mbar_try_wait(bar, parity)) return;
-  for (int i = 0; i < kSpinLimit; ++i) {
+  for (int i = 0; i < limit; ++i) {
     __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return;
   }

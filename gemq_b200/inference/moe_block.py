@@ -118,6 +118,23 @@ class _QuantFusedMoEBase(nn.Module):
             self._scratch.data_ptr(), self._scratch.numel(), stream_ptr(dev)))
         return out, w, idx
 
+    def _scratch_word(self, fn) -> Tensor:
+        off = fn(self._scratch.data_ptr()) - self._scratch.data_ptr()
+        return self._scratch[off:off + 4].view(torch.int32)
+
+    def decode_error_code(self, clear: bool = True) -> int:
+        """Error word of the decode scratch (0 = every bounded wait was met and every expert id was
+        in range); synchronises.  After a non-zero code call ``reset_decode_scratch``."""
+        word = self._scratch_word(_capi.lib.gemq_workspace_error_word)
+        code = int(word.item())
+        if clear and code:
+            word.zero_()
+        return code
+
+    def reset_decode_scratch(self) -> None:
+        """Put the decode scratch back into its resting state (all zero)."""
+        self._scratch.zero_()
+
     def _route(self, x: Tensor, mode: int, renorm: bool):
         dev = require_cuda(x)
         T, D = x.shape

@@ -87,6 +87,8 @@ typedef struct {
   const int32_t* zs_strides; /* [E] element offsets into scales/zeros, or NULL: expert e starts at row e*(K/G) */
   int64_t wq_rows;           /* rows (dim 0) of the stacked wq tensor */
   int64_t zs_rows;           /* rows (dim 0) of the stacked scales / zeros tensors */
+  int32_t n_experts;         /* E, or 0 when unknown: expert ids read on the device are clamped into [0, E) and an
+                                id outside it is reported through the workspace's error word */
 } gemq_stacked_t;
 
 /* dequant_sel_splitk_gemv_triton (dequant_gemv.py:225-270): expert idx[0] of stacked tensors
@@ -132,6 +134,19 @@ int gemq_dequant_group_gemv(const void* x, int ldx, const int64_t* indices, int 
 int gemq_moe_route(const void* x, const void* gate, int tokens, int D, int E, int A,
                    int mode, int renorm, int x_is_bf16,
                    int64_t* idx, void* weights, float* logits, gemq_stream_t stream);
+
+/* Device address of the int32 error word inside a GEMV-family workspace (also the head of the
+ * scratch of gemq_moe_decode).  The decode kernels bound every wait on another CTA or warp; when
+ * one runs out, or an expert id read on the device lies outside [0, E), the kernel records a
+ * non-zero code here and still returns (its output is then undefined).  0 = nothing happened.
+ * After a non-zero code zero-fill the workspace before its next use: the counters and partial
+ * sums it holds are no longer in their resting state.  The caller reads and clears the word. */
+int32_t* gemq_workspace_error_word(void* workspace);
+
+/* Device address of an int32 the one-launch decode layer reads at start: the number of polls a
+ * bounded wait may take (0 = the built-in limit, about 2^18).  Exists so that the expiry path can
+ * be exercised from the host without a stuck kernel. */
+int32_t* gemq_workspace_wait_limit_word(void* workspace);
 
 /* ---- whole decode layer --------------------------------------------------------------- */
 
