@@ -13,6 +13,7 @@ import torch
 
 from .inference.moe_block import QuantFusedDeepseekV2MoEBlock, QuantFusedMixtralMoEBlock
 from .inference.packed_linear import PackedLinear
+from .synth_bits import draw_expert_bits  # noqa: F401  (re-exported)
 
 MIXTRAL_8X7B = dict(hidden_size=4096, intermediate_size=14336, num_local_experts=8, num_experts_per_tok=2)
 DEEPSEEK_V2_LITE = dict(hidden_size=2048, moe_intermediate_size=1408, n_routed_experts=64, n_shared_experts=2,
@@ -36,15 +37,6 @@ def draw_codes_meta(out_f: int, in_f: int, nbits: int, group: int, gen: torch.Ge
 def make_linear(out_f: int, in_f: int, nbits: int, group: int, gen: torch.Generator, device) -> PackedLinear:
     codes, scale, zero = draw_codes_meta(out_f, in_f, nbits, group, gen, device)
     return PackedLinear.from_codes(codes, scale, zero, nbits, group)
-
-
-def draw_expert_bits(n_experts: int, seed: int, lo: float = 1.5, hi: float = 2.5):
-    """Per-expert bit-widths from {1,2,3,4} whose mean lies in [lo, hi]."""
-    g = torch.Generator().manual_seed(seed)
-    while True:
-        bits = torch.randint(1, 5, (n_experts,), generator=g).tolist()
-        if lo <= sum(bits) / n_experts <= hi:
-            return bits
 
 
 def mixtral_block(seed: int = 0, device="cuda", bits=None, group: int = 128, **overrides) -> QuantFusedMixtralMoEBlock:
@@ -76,22 +68,27 @@ def deepseek_block(seed: int = 0, device="cuda", bits=None, shared_bits: int = 4
 
 
 def mixtral_expert_parallel(rank: int, world: int, seed: int = 0, device="cuda", bits=None, group: int = 128,
-                            process_group=None, **overrides):
-    """This rank's shard of a Mixtral-shaped layer: experts ``[rank*E/world, (rank+1)*E/world)``.
-    Every expert is drawn from its own seed, so all ranks agree on the full layer."""
-    from .inference.expert_parallel import ExpertParallelMixtralMoE
+                            process_group=None, routed_rows=None, **overrides):
+    """This rank's shard of a Mixtral-shaped layer.  Without ``routed_rows`` rank r holds experts
+    ``[r*E/world, (r+1)*E/world)``; with it (rows each expert receives, e.g. from calibration) the
+    experts are placed so that the rows per rank even out.  Every expert is drawn from its own
+    seed, so all ranks agree on the full layer.  Returns (layer, bits, expert -> rank list)."""
+    from .inference.expert_parallel import ExpertParallelMixtralMoE, balanced_placement, contiguous_placement
     cfg = {**MIXTRAL_8X7B, **overrides}
     E, D, Fd, A = cfg["num_local_experts"], cfg["hidden_size"], cfg["intermediate_size"], cfg["num_experts_per_tok"]
-    assert E % world == 0
     bits = bits or draw_expert_bits(E, seed)
     gate = (torch.randn(E, D, device=device, generator=generator(seed, device)) * 0.02).to(torch.float16)
-    lo, hi = rank * E // world, (rank + 1) * E // world
+    place = balanced_placement(routed_rows, world) if routed_rows is not None else contiguous_placement(E, world)
+    mine = [e for e in range(E) if int(place[e]) == rank]
     w1, w2, w3 = [], [], []
-    for e in range(lo, hi):
+    for e in mine:
         gen = generator(seed * 1000 + 17 * e + 1, device)
         w1.append(make_linear(Fd, D, bits[e], group, gen, device))
         w3.append(make_linear(Fd, D, bits[e], group, gen, device))
         w2.append(make_linear(D, Fd, bits[e], group, gen, device))
-    local_cfg = SimpleNamespace(hidden_size=D, intermediate_size=Fd, num_local_experts=hi - lo, num_experts_per_tok=1)
-    local = QuantFusedMixtralMoEBlock.from_linears(local_cfg, gate[lo:hi].clone(), w1, w2, w3)
-    return ExpertParallelMixtralMoE(local, gate, E, A, process_group), bits
+    local = None
+    if mine:
+        local_cfg = SimpleNamespace(hidden_size=D, intermediate_size=Fd, num_local_experts=len(mine), num_experts_per_tok=1)
+        local = QuantFusedMixtralMoEBlock.from_linears(local_cfg, gate[mine].clone(), w1, w2, w3)
+    layer = ExpertParallelMixtralMoE(local, gate, E, A, process_group, expert_to_rank=place)
+    return layer, bits, place.tolist()

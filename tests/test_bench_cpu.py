@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_reference_arm_prints_one_json_line():
     out = subprocess.run(
         [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1",
-         "--cpu-sample-cols", "128"],
+         "--shape", "256,512"],
         cwd=ROOT, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
@@ -21,4 +21,5 @@ def test_reference_arm_prints_one_json_line():
     assert base["kind"] == "port" and base["cores"] >= 1 and base["value"] == line["value"]
     e2e = line["e2e"]
     assert e2e["value"] == line["value"] and e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
-    assert "workload" in line["config"]
+    assert "workload" in line["config"] and line["config"]["hidden"] == 256
+    assert base["cores"] == len(os.sched_getaffinity(0))

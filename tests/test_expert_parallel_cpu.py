@@ -7,7 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from gemq_b200.inference.expert_parallel import combine_in_expert_order, dispatch_plan, expert_parallel_forward
+from gemq_b200.inference.expert_parallel import (balanced_placement, combine_in_expert_order, dispatch_plan,
+                                                 expert_parallel_forward, local_ids)
 
 E, A, D = 8, 2, 16
 
@@ -43,22 +44,46 @@ def test_dispatch_plan_groups_by_rank():
     assert sorted(order.tolist()) == list(range(37 * A))
 
 
-def _worker(rank, world, port, results):
+def test_balanced_placement_evens_out_rows():
+    rows = [4000, 2500, 700, 400, 300, 200, 60, 32]  # skewed popularity, as Dirichlet(0.5) gives
+    place = balanced_placement(rows, 2)
+    per_rank = [sum(r for r, p in zip(rows, place.tolist()) if p == k) for k in range(2)]
+    assert max(per_rank) / sum(rows) < 0.52  # contiguous halves would put 93 % on rank 0
+    assert place.tolist() == balanced_placement(rows, 2).tolist()
+    loc = local_ids(place)
+    for k in range(2):
+        mine = [e for e in range(8) if place[e] == k]
+        assert [int(loc[e]) for e in mine] == list(range(len(mine)))
+    # eight ranks, eight experts: one expert each, the hottest rank holds the hottest expert
+    assert sorted(balanced_placement(rows, 8).tolist()) == list(range(8))
+
+
+def test_dispatch_plan_with_placement_groups_by_rank():
+    _, _, sel = make_inputs(1, 29)
+    place = torch.tensor([1, 0, 0, 1, 0, 1, 1, 0])
+    order, counts, es = dispatch_plan(sel, E, 2, place)
+    dest = place[es]
+    assert torch.all(dest[1:] >= dest[:-1]) and torch.equal(torch.bincount(dest, minlength=2), counts)
+    assert sorted(order.tolist()) == list(range(29 * A))
+
+
+def _worker(rank, world, port, results, placement=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    per_rank = E // world
+    place = torch.tensor(placement) if placement is not None else torch.arange(E) // (E // world)
+    mine = [e for e in range(E) if int(place[e]) == rank]
     T = 11 + 3 * rank  # ragged token counts per rank
     x, w, sel = make_inputs(100 + rank, T)
 
     def local_ffn(rows, local_e, wts):
         out = torch.empty_like(rows)
         for i in range(rows.shape[0]):
-            e_global = rank * per_rank + int(local_e[i])
+            e_global = mine[int(local_e[i])]
             out[i] = (toy_expert(rows[i].float(), e_global) * float(wts[i])).to(rows.dtype)
         return out
 
-    y = expert_parallel_forward(x, w, sel, E, local_ffn)
+    y = expert_parallel_forward(x, w, sel, E, local_ffn, expert_to_rank=None if placement is None else place)
     ref = single_process(x, w, sel)
     results[rank] = bool(torch.equal(y, ref))
     dist.barrier()
@@ -71,6 +96,16 @@ def test_expert_parallel_matches_single_process_gloo():
     results = mgr.dict()
     port = 29500 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}
+
+
+def test_expert_parallel_with_uneven_placement_gloo():
+    """Rank 0 holds two experts, rank 1 six: ids travel as positions inside the owner's expert list."""
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, results, [1, 0, 1, 1, 0, 1, 1, 1]), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
 
 

@@ -203,8 +203,11 @@ def _ep_worker(rank, world, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     dims = dict(hidden_size=256, intermediate_size=512, num_local_experts=4, num_experts_per_tok=2)
     bits = [1, 2, 3, 4]
-    ep, _ = synth.mixtral_expert_parallel(rank, world, seed=5, device=dev, bits=bits, **dims)
-    full, _ = synth.mixtral_expert_parallel(0, 1, seed=5, device=dev, bits=bits, **dims)  # all experts, no exchange
+    # experts placed by (made-up) routed-row statistics: rank 0 holds expert 0 alone, rank 1 the other three
+    ep, _, place = synth.mixtral_expert_parallel(rank, world, seed=5, device=dev, bits=bits, routed_rows=[90, 40, 30, 20],
+                                                 **dims)
+    assert place == [0, 1, 1, 1]
+    full, _, _ = synth.mixtral_expert_parallel(0, 1, seed=5, device=dev, bits=bits, **dims)  # all experts, no exchange
     g = torch.Generator().manual_seed(11 + rank)
     T = 150 + 20 * rank
     x = torch.randn(T, 256, generator=g).half().to(dev)
