@@ -2,8 +2,8 @@
 //
 // Some hosts of this library own no allocator they may call on the hot path: a serving
 // process whose memory pool is frozen after start-up, a plugin loaded into a runtime that
-// forbids cudaMalloc once the model is resident, code running while a CUDA graph is being
-// captured.  They can still pass inputs and outputs, but not the zero-initialised split-K
+// forbids cudaMalloc once the model is resident.  They can still pass inputs and outputs, but
+// not the zero-initialised split-K
 // workspace the other GEMV entry points ask for.  This variant keeps that workspace in a
 // fixed array that is part of the library image, so it exists (2 MiB on every GPU that
 // loads the library, until the process exits) without any allocation call.
@@ -19,7 +19,8 @@ constexpr size_t kStaticScratchBytes = 2u << 20;  // 32 KB of arrival counters +
 // cudaGetSymbolAddress -- it is NOT a device address and must never be handed to a kernel.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-// Device address of the array on the current device, looked up once per device.
+// Device address of the array on the current device, looked up once per device.  The device
+// of the stream a caller passes must be the current one: the lookup resolves against it.
 static int static_scratch_ptr(void** out) {
   static std::mutex mu;
   static void* cached[64] = {nullptr};

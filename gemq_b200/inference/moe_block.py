@@ -9,6 +9,9 @@ gate/up, SiLU*mul + down, combine); the routing result never reaches the host.
 from __future__ import annotations
 
 import ctypes as C
+import itertools
+import weakref
+from typing import Tuple
 
 import torch
 import torch.nn as nn
@@ -17,6 +20,7 @@ from torch import Tensor
 
 from .. import _capi
 from ..kernels import dequant_gemm, dequant_group_gemm
+from ..kernels._ops import library_op
 from ..kernels._runtime import require_cuda, stream_ptr
 from .packed_linear import is_packed_linear
 
@@ -30,7 +34,20 @@ def _excl_cumsum(vals, device):
     return t.to(torch.int32).to(device)
 
 
-def route_tokens(x: Tensor, gate_weight: Tensor, top_k: int, mode: int, renorm: bool):
+# The block-level library calls take a ctypes description of the layer; as custom operators
+# they receive an integer handle of the block instead (dynamo treats it as a constant).
+_BLOCKS: "weakref.WeakValueDictionary[int, _QuantFusedMoEBase]" = weakref.WeakValueDictionary()
+_HANDLES = itertools.count(1)
+
+
+def _fake_route(x, gate_weight, top_k, mode, renorm):
+    T = x.shape[0]
+    return (x.new_empty((T, top_k)), x.new_empty((T, top_k), dtype=torch.int64),
+            x.new_empty((T, gate_weight.shape[0]), dtype=torch.float32))
+
+
+@library_op("moe_route", _fake_route)
+def route_tokens(x: Tensor, gate_weight: Tensor, top_k: int, mode: int, renorm: bool) -> Tuple[Tensor, Tensor, Tensor]:
     """Router on the device: ``(weights [T, A] in x.dtype, indices int64 [T, A], logits fp32 [T, E])``."""
     dev = require_cuda(x, gate_weight)
     T, D = x.shape
@@ -104,10 +121,15 @@ class _QuantFusedMoEBase(nn.Module):
         self._layer = L
         nbytes = _capi.lib.gemq_moe_decode_scratch_bytes(C.byref(L))
         self._scratch = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        self._handle = next(_HANDLES)
+        _BLOCKS[self._handle] = self
 
     # -- forward pieces ----------------------------------------------------------------
     def _decode(self, x: Tensor, route_mode: int):
         """``x [T, D]`` fp16 -> ``out [T, D]``, routing weights and indices, all on the device."""
+        return _moe_decode(x, self._handle, route_mode)
+
+    def _decode_impl(self, x: Tensor, route_mode: int):
         dev = require_cuda(x)
         T = x.shape[0]
         out = torch.empty_like(x)
@@ -136,16 +158,7 @@ class _QuantFusedMoEBase(nn.Module):
         self._scratch.zero_()
 
     def _route(self, x: Tensor, mode: int, renorm: bool):
-        dev = require_cuda(x)
-        T, D = x.shape
-        idx = torch.empty((T, self.top_k), dtype=torch.int64, device=dev)
-        w = torch.empty((T, self.top_k), dtype=x.dtype, device=dev)
-        logits = torch.empty((T, self.num_experts), dtype=torch.float32, device=dev)
-        gate = self.gate.weight if x.dtype == torch.float16 else self.gate.weight.to(x.dtype)
-        _capi.check("gemq_moe_route", _capi.lib.gemq_moe_route(
-            x.data_ptr(), gate.data_ptr(), T, D, self.num_experts, self.top_k, mode, int(renorm),
-            int(x.dtype == torch.bfloat16), idx.data_ptr(), w.data_ptr(), logits.data_ptr(), stream_ptr(dev)))
-        return w, idx, logits
+        return route_tokens(x, self.gate.weight, self.top_k, mode, renorm)
 
     def _prefill_ok(self) -> bool:
         D, Fd, G = self.hidden_dim, self.ffn_dim, self.block_group_size
@@ -157,6 +170,12 @@ class _QuantFusedMoEBase(nn.Module):
         """``x [T, D]`` fp16/bf16 -> ``(out, weights, indices, logits)`` through the expert-sorted
         tcgen05 grouped GEMM; no host synchronisation.  ``routing = (weights [T, A] in x.dtype,
         indices int64 [T, A])`` skips the router."""
+        if routing is None:
+            return _moe_prefill(x, self._handle, route_mode, renorm)
+        out = _moe_prefill_routed(x, routing[0], routing[1], self._handle, route_mode, renorm)
+        return out, routing[0], routing[1], None
+
+    def _prefill_impl(self, x: Tensor, route_mode: int, renorm: bool, routing=None):
         dev = require_cuda(x)
         x = x.contiguous()
         T = x.shape[0]
@@ -199,18 +218,40 @@ class _QuantFusedMoEBase(nn.Module):
         return dequant_group_gemm(F.silu(x1) * x3, expert_idx, self.w2_wq, self.w2_scales, self.w2_zeros,
                                   self.w2_nbits, self.w2_group_sizes, self.w2_wq_strides, self.w2_zs_strides)[0]
 
-    def _experts_n_tokens(self, x: Tensor, routing_weights: Tensor, selected: Tensor) -> Tensor:
-        """Per-expert gather / FFN / weighted scatter-add of the n-token path
-        (gemq/inference/moe_block.py:182-195)."""
-        xh = x if x.dtype == torch.float16 else x.to(torch.float16)
-        final = torch.zeros_like(x)
-        expert_mask = F.one_hot(selected, num_classes=self.num_experts).permute(2, 1, 0)
-        expert_hit = torch.greater(expert_mask.sum(dim=(-1, -2)), 0).nonzero()
-        for expert_idx in expert_hit:
-            slot, top_x = torch.where(expert_mask[expert_idx].squeeze(0))
-            cur = self.forward_single_expert(expert_idx, xh[top_x]).to(x.dtype) * routing_weights[top_x, slot, None]
-            final.index_add_(0, top_x, cur.to(x.dtype))
-        return final
+    def _unsupported(self, x: Tensor) -> ValueError:
+        return ValueError(
+            f"n-token forward needs hidden / intermediate sizes that are multiples of 128, a group size that is a "
+            f"multiple of 64, at most 8 experts per token and 256 experts, and fp16 or bf16 activations; got hidden="
+            f"{self.hidden_dim}, intermediate={self.ffn_dim}, group={self.block_group_size}, top_k={self.top_k}, "
+            f"experts={self.num_experts}, dtype={x.dtype}")
+
+
+def _fake_decode(x, handle, route_mode):
+    k = _BLOCKS[handle].top_k
+    return (torch.empty_like(x), x.new_empty((x.shape[0], k), dtype=torch.float16),
+            x.new_empty((x.shape[0], k), dtype=torch.int64))
+
+
+@library_op("moe_decode", _fake_decode)
+def _moe_decode(x: Tensor, handle: int, route_mode: int) -> Tuple[Tensor, Tensor, Tensor]:
+    return _BLOCKS[handle]._decode_impl(x, route_mode)
+
+
+def _fake_prefill(x, handle, route_mode, renorm):
+    blk = _BLOCKS[handle]
+    T = x.shape[0]
+    return (torch.empty_like(x), x.new_empty((T, blk.top_k)), x.new_empty((T, blk.top_k), dtype=torch.int64),
+            x.new_empty((T, blk.num_experts), dtype=torch.float32))
+
+
+@library_op("moe_prefill", _fake_prefill)
+def _moe_prefill(x: Tensor, handle: int, route_mode: int, renorm: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    return _BLOCKS[handle]._prefill_impl(x, route_mode, renorm)
+
+
+@library_op("moe_prefill_routed", lambda x, w, idx, handle, route_mode, renorm: torch.empty_like(x))
+def _moe_prefill_routed(x: Tensor, w: Tensor, idx: Tensor, handle: int, route_mode: int, renorm: bool) -> Tensor:
+    return _BLOCKS[handle]._prefill_impl(x, route_mode, renorm, routing=(w, idx))[0]
 
 
 class QuantFusedMixtralMoEBlock(_QuantFusedMoEBase):
@@ -251,9 +292,7 @@ class QuantFusedMixtralMoEBlock(_QuantFusedMoEBase):
         if self._prefill_ok() and x.dtype in (torch.float16, torch.bfloat16):
             out, _, _, logits = self._prefill(x, ROUTE_FP32_SOFTMAX, True)
             return out.reshape(b, s, d), logits.to(hidden_states.dtype)
-        rw, sel, logits = self._route(x, ROUTE_FP32_SOFTMAX, True)
-        out = self._experts_n_tokens(x, rw, sel)
-        return out.reshape(b, s, d), logits.to(hidden_states.dtype)
+        raise self._unsupported(x)
 
     def forward_one_token(self, hidden_states: Tensor):
         """gemq/inference/moe_block.py:200-235."""
@@ -335,11 +374,7 @@ class QuantFusedDeepseekV2MoEBlock(_QuantFusedMoEBase):
         if self._prefill_ok() and x.dtype in (torch.float16, torch.bfloat16):
             out, _, _, _ = self._prefill(x, ROUTE_FP32, bool(self.norm_topk_prob))
             return out.reshape(b, s, d)
-        rw, sel, _ = self._route(x, ROUTE_FP32, bool(self.norm_topk_prob))
-        out = self._experts_n_tokens(x, rw, sel)
-        xh = x if x.dtype == torch.float16 else x.to(torch.float16)
-        out = out + self._shared_ffn(xh).to(x.dtype)
-        return out.reshape(b, s, d)
+        raise self._unsupported(x)
 
     def forward_one_token(self, hidden_states: Tensor) -> Tensor:
         """gemq/inference/moe_block.py:488-531."""

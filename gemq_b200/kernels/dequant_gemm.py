@@ -5,12 +5,21 @@ import torch
 from torch import Tensor
 
 from .. import _capi
+from ._ops import library_op
 from ._runtime import check_kernel_form, error_word, require, require_cuda, stream_ptr, tc_gemm_ok
 from .dequant_gemv import dequant_gemv_rows
 
 _ROW_BLOCK = 64
 
 
+def _fake_gemm(x, w_q, scales, zeros, nbits, group_size):
+    M, K = x.shape
+    N = w_q.shape[1]
+    tc = tc_gemm_ok(M, N, K, group_size) and x.dtype in (torch.float16, torch.bfloat16)
+    return x.new_empty((M, N), dtype=x.dtype if tc else torch.float16)
+
+
+@library_op("dequant_gemm", _fake_gemm)
 def dequant_gemm(x: Tensor, w_q: Tensor, scales: Tensor, zeros: Tensor, nbits: int, group_size: int) -> Tensor:
     """``output[M, N] = x[M, K] @ dequantize(w_q, scales, zeros)``, fp16
     (gemq/triton_kernels/dequant_gemm.py:150-193).  32 rows or more go to the tcgen05 GEMM when
@@ -29,9 +38,10 @@ def dequant_gemm(x: Tensor, w_q: Tensor, scales: Tensor, zeros: Tensor, nbits: i
             out.data_ptr(), M, N, K, group_size, int(x.dtype == torch.bfloat16), error_word(dev).data_ptr(),
             stream_ptr(dev)))
         return out
+    rows = dequant_gemv_rows._init_fn  # the plain function behind the operator
     if M <= _ROW_BLOCK:
-        return dequant_gemv_rows(x, w_q, scales, zeros, nbits, group_size)
-    return torch.cat([dequant_gemv_rows(x[i:i + _ROW_BLOCK], w_q, scales, zeros, nbits, group_size)
+        return rows(x, w_q, scales, zeros, nbits, group_size)
+    return torch.cat([rows(x[i:i + _ROW_BLOCK], w_q, scales, zeros, nbits, group_size)
                       for i in range(0, M, _ROW_BLOCK)])
 
 

@@ -7,9 +7,15 @@ import torch
 from torch import Tensor
 
 from .. import _capi
+from ._ops import library_op
 from ._runtime import check_kernel_form, gemv_workspace, require, require_cuda, stream_ptr
 
 
+def _fake_rows(x, w_q, scales, zeros, nbits, group_size):
+    return x.new_empty((x.shape[0], w_q.shape[1]), dtype=torch.float16)
+
+
+@library_op("dequant_gemv_rows", _fake_rows)
 def dequant_gemv_rows(x: Tensor, w_q: Tensor, scales: Tensor, zeros: Tensor, nbits: int, group_size: int) -> Tensor:
     """``x[M, K] @ deq(w_q)`` for a few rows (decode batch); fp16 in, fp16 out."""
     dev = require_cuda(x, w_q, scales, zeros)
@@ -26,14 +32,18 @@ def dequant_gemv_rows(x: Tensor, w_q: Tensor, scales: Tensor, zeros: Tensor, nbi
     return out
 
 
+@library_op("dequant_splitk_gemv", _fake_rows)
 def dequant_splitk_gemv(x: Tensor, w_q: Tensor, scales: Tensor, zeros: Tensor, nbits: int, group_size: int) -> Tensor:
     """``output[1, N] = x[1, K] @ dequantize(w_q, scales, zeros)``
     (gemq/triton_kernels/dequant_gemv.py:118-156).  Unlike the reference's fp16 atomics the
     split-K sum is formed in a fixed order, so the result is reproducible."""
     require(x.dim() == 2 and x.shape[0] == 1, "dequant_splitk_gemv takes exactly one row (M == 1)")
-    return dequant_gemv_rows(x, w_q, scales, zeros, nbits, group_size)
+    return dequant_gemv_rows._init_fn(x, w_q, scales, zeros, nbits, group_size)
 
 
+@library_op("dequant_sel_splitk_gemv",
+            lambda x, idx, w_q, scales, zeros, nbits, wq_strides, group_size:
+            x.new_empty((1, w_q.shape[1]), dtype=torch.float16))
 def dequant_sel_splitk_gemv(x: Tensor, idx: Tensor, w_q: Tensor, scales: Tensor, zeros: Tensor,
                             nbits: Tensor, wq_strides: Tensor, group_size: int) -> Tensor:
     """GEMV against expert ``idx[0]`` of stacked tensors (gemq/triton_kernels/dequant_gemv.py:225-270)."""

@@ -8,6 +8,7 @@ import torch
 from torch import Tensor
 
 from .. import _capi
+from ._ops import library_op
 from ._runtime import error_word, gemv_workspace, require, require_cuda, stream_ptr, tc_gemm_ok
 
 _ROW_BLOCK = 64
@@ -32,8 +33,16 @@ def dequant_group_gemm(x: Tensor, indices: Tensor, wq: Tensor, scales: Tensor, z
                        compute_dtype=torch.float16) -> Tensor:
     """``output[g] = x @ dequantize(W[indices[g]])`` -> ``[A, M, N]``
     (gemq/triton_kernels/dequant_group_gemm.py:155-202)."""
-    dev = require_cuda(x, indices, wq, scales, zeros, nbits, group_sizes, wq_strides, zs_strides)
     require(compute_dtype == torch.float16, "only float16 is supported, as in the reference kernel")
+    return _group_gemm(x, indices, wq, scales, zeros, nbits, group_sizes, wq_strides, zs_strides)
+
+
+@library_op("dequant_group_gemm",
+            lambda x, indices, wq, scales, zeros, nbits, group_sizes, wq_strides, zs_strides:
+            x.new_empty((indices.numel(), x.shape[0], wq.shape[1]), dtype=torch.float16))
+def _group_gemm(x: Tensor, indices: Tensor, wq: Tensor, scales: Tensor, zeros: Tensor,
+                nbits: Tensor, group_sizes: Tensor, wq_strides: Tensor, zs_strides: Tensor) -> Tensor:
+    dev = require_cuda(x, indices, wq, scales, zeros, nbits, group_sizes, wq_strides, zs_strides)
     require(x.dim() == 2 and x.dtype == torch.float16, "x must be float16 [M, K]")
     require(indices.dtype == torch.int64, "indices must be int64")
     indices = indices.reshape(-1)

@@ -3,11 +3,13 @@ signatures as gemq/triton_kernels/fused_dequant_bmm.py."""
 from __future__ import annotations
 
 import ctypes
+from typing import Tuple
 
 import torch
 from torch import Tensor
 
 from .. import _capi
+from ._ops import library_op
 from ._runtime import gemv_workspace, require, require_cuda, stream_ptr
 
 
@@ -18,9 +20,15 @@ def _check_stacked(w, s, z, nbits, strides):
     require(nbits.dtype == torch.int32 and strides.dtype == torch.int32, "nbits / strides must be int32")
 
 
+def _fake_up(x, idx, w1, w3, w1_scales, w1_zeros, w3_scales, w3_zeros, nbits, w_strides, group_size):
+    n = idx.shape[0] * w1.shape[1]
+    return x.new_empty((1, n), dtype=torch.float16), x.new_empty((1, n), dtype=torch.float16)
+
+
+@library_op("fused_dequant_up_proj", _fake_up)
 def fused_dequant_up_proj(x: Tensor, idx: Tensor, w1: Tensor, w3: Tensor,
                           w1_scales: Tensor, w1_zeros: Tensor, w3_scales: Tensor, w3_zeros: Tensor,
-                          nbits: Tensor, w_strides: Tensor, group_size: int):
+                          nbits: Tensor, w_strides: Tensor, group_size: int) -> Tuple[Tensor, Tensor]:
     """``x1, x3 [1, A*N]``: ``x @ deq(w1[e])`` and ``x @ deq(w3[e])`` for ``e`` in ``idx``
     (gemq/triton_kernels/fused_dequant_bmm.py:122-173)."""
     dev = require_cuda(x, idx, w1, w3, w1_scales, w1_zeros, w3_scales, w3_zeros, nbits, w_strides)
@@ -43,6 +51,9 @@ def fused_dequant_up_proj(x: Tensor, idx: Tensor, w1: Tensor, w3: Tensor,
     return x1, x3
 
 
+@library_op("fused_dequant_down_proj",
+            lambda x1, x3, idx, w2, w2_scales, w2_zeros, nbits, w_strides, group_size:
+            x1.new_empty((1, idx.shape[0] * w2.shape[1]), dtype=torch.float16))
 def fused_dequant_down_proj(x1: Tensor, x3: Tensor, idx: Tensor, w2: Tensor,
                             w2_scales: Tensor, w2_zeros: Tensor, nbits: Tensor, w_strides: Tensor,
                             group_size: int) -> Tensor:

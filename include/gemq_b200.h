@@ -224,15 +224,21 @@ const int32_t* gemq_moe_prefill_error_word(const gemq_moe_layer_t* layer, int to
 /* No counterpart in the reference.  y[1, N] = x[1, K] @ deq(wq), the same result as
  * gemq_dequant_gemv with tokens == 1, but without a caller-provided workspace: the split-K
  * scratch lives in a fixed 2 MiB device array inside the library (gemq_static_scratch_bytes),
- * held by every GPU that loads the library until the process exits.  Nothing is allocated
- * or freed, here or in anything it calls.  For hosts that must not allocate on this path: a
- * serving process with a frozen memory pool, a plugin inside a runtime that forbids
- * cudaMalloc after start-up, code running during stream capture.
+ * held by every GPU that loads the library until the process exits.  No device memory is
+ * allocated or freed, here or in anything it calls.  For hosts that must not allocate device
+ * memory on this path: a serving process with a frozen memory pool, a plugin inside a runtime
+ * that forbids cudaMalloc after start-up.
  *   - Returns GEMQ_ERR_WORKSPACE when gemq_gemv_workspace_bytes(N, K, 1) exceeds the array
- *     (roughly N * ceil(K / 512) > 490,000), GEMQ_ERR_BAD_ARG on null pointers or bad extents.
+ *     (roughly N * ceil(K / 512) > 490,000; the sizing rule reserves room for an activation
+ *     staging area this entry point does not use, so the limit is a little conservative),
+ *     GEMQ_ERR_BAD_ARG on null pointers or bad extents.
  *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with that device current); make that first call outside any
- *     stream capture.
+ *     (cudaGetSymbolAddress), and the first launch of each kernel on a device sets its
+ *     shared-memory attribute; the first use of a weight tensor adds an entry to a small
+ *     host-side cache of TMA descriptors (host heap only).  Make the first call for a device and
+ *     a weight tensor outside any stream capture.
+ *   - The device that owns `stream` must be the current device of the calling thread: the
+ *     array's address is looked up for the current device.
  *   - All calls on a device share the one array, and the array keeps what the last call left
  *     in it; every call first clears the part it reads.  Two calls that overlap on the GPU
  *     (different streams, no ordering between them) race on it: order them. */

@@ -232,3 +232,25 @@ def test_expert_id_out_of_range_is_reported_not_used():
     ref = O.moe_reference_fp32(xs.cpu()[good], ws[good].float(), sel[good], w1, w3, w2).numpy()
     got = out.float().cpu().numpy()[good]
     assert rel_fro(got, ref) < REL_FRO_TOL and max_abs(got, ref) < MAX_ABS_TOL
+
+
+def test_torch_compile_traces_through_the_block():
+    """torch.compile(mode="reduce-overhead", fullgraph=True) of the one-token forward, as the
+    reference's decode step is compiled (gemq/benchmark_generate.py:158-160): no graph break,
+    same bits as eager."""
+    import torch._dynamo
+    layer = MF.make_layer("mixtral", D=512, Fd=1024, E=4, A=2, bits=[1, 2, 3, 4], seed=51, gate_std=0.02)
+    blk = MF.gpu_block(layer)
+    x = torch.randn(1, 1, 512, generator=torch.Generator().manual_seed(51)).half().cuda()
+    eager, _ = blk(x)
+
+    def step(h):
+        return blk(h)[0]
+
+    explained = torch._dynamo.explain(step)(x)
+    assert explained.graph_break_count == 0, explained.break_reasons
+    compiled = torch.compile(step, mode="reduce-overhead", fullgraph=True)
+    for _ in range(3):  # warm-up, capture, replay
+        out = compiled(x)
+    assert torch.equal(out, eager)
+    torch._dynamo.reset()

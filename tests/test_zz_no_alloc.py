@@ -45,6 +45,47 @@ def test_static_scratch_gemv_matches_workspace_gemv_twice():
         g, w = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert rel_fro(g, w) < REL_FRO_TOL and max_abs(g, w) < MAX_ABS_TOL
         assert torch.equal(got, want)  # same kernel, same fixed summation order
+        ref = O.dequant_gemv(x.cpu().numpy(), wq.cpu().numpy(), s.cpu().numpy(), z.cpu().numpy(), b, 128)
+        assert rel_fro(g, ref) < REL_FRO_TOL and max_abs(g, ref) < MAX_ABS_TOL  # and the oracle agrees
+
+
+@pytest.mark.parametrize("case", ["unaligned_x", "n_not_multiple_of_32", "group_64"])
+def test_static_scratch_gemv_fallback_shapes(case):
+    """Shapes the persistent kernel does not take reach the other kernels behind the same entry
+    point: an activation that is not 16-byte aligned, an N that is not a multiple of 32, a group
+    size of 64.  Each must match gemq_dequant_gemv on a caller workspace."""
+    from gemq_b200 import _capi
+    from gemq_b200.kernels._runtime import gemv_workspace
+    lib = _capi.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    N, K, b, G = (2048, 1024, 2, 128)
+    if case == "n_not_multiple_of_32":
+        N = 2000
+    if case == "group_64":
+        G = 64
+    rng = np.random.default_rng(7)
+    q = rng.integers(0, 2 ** b, (N, K), dtype=np.uint8)
+    s = (np.abs(rng.standard_normal((K // G, N))) * 0.01 + 1e-3).astype(np.float16)
+    z = O.kernel_form_offset(s, (rng.random((K // G, N)) * (2 ** b - 1)).astype(np.float16))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    wq, s, z = dev(O.pack_kernel_form(q, b)), dev(s), dev(z)
+    xbuf = dev(rng.standard_normal(K + 8).astype(np.float16))
+    x = xbuf[1:1 + K] if case == "unaligned_x" else xbuf[:K]
+    assert (x.data_ptr() % 16 != 0) == (case == "unaligned_x")
+    got = torch.empty((1, N), dtype=torch.float16, device="cuda")
+    want = torch.empty((1, N), dtype=torch.float16, device="cuda")
+    ws = gemv_workspace(got.device, N, K, 1)
+    rc = lib.gemq_dequant_gemv(x.data_ptr(), K, wq.data_ptr(), s.data_ptr(), z.data_ptr(), want.data_ptr(), N, 1, N, K, b, G,
+                               ws.data_ptr(), ws.numel(), stream)
+    assert rc == 0
+    rc = lib.gemq_dequant_gemv_static(x.data_ptr(), wq.data_ptr(), s.data_ptr(), z.data_ptr(), got.data_ptr(), N, K, b, G,
+                                      stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    ref = O.dequant_gemv(x.cpu().numpy()[None, :], wq.cpu().numpy(), s.cpu().numpy(), z.cpu().numpy(), b, G)
+    g = got.float().cpu().numpy()
+    assert rel_fro(g, ref) < REL_FRO_TOL and max_abs(g, ref) < MAX_ABS_TOL
 
 
 def test_static_scratch_rejects_oversized_problem():
