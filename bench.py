@@ -46,8 +46,11 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=8)
     p.add_argument("--no-prefill", action="store_true", help="leave the config-3 sub-record out")
-    p.add_argument("--mode", default="bench", choices=["bench", "layer_only", "prefill_only"],
-                   help="layer_only / prefill_only: a short eager loop of one op for profilers; prints its own timing")
+    p.add_argument("--mode", default="bench", choices=["bench", "layer_only", "prefill_only", "generate"],
+                   help="layer_only / prefill_only: a short eager loop of one op for profilers; generate: the full "
+                        "32-layer decoder (config 4), 512-token prompt, 256 greedy tokens; each prints its own JSON")
+    p.add_argument("--batch", type=int, default=1, help="generate mode: sequences decoded together")
+    p.add_argument("--gen-layers", type=int, default=32)
     p.add_argument("--prefill-tokens", type=int, default=4096)
     p.add_argument("--shape", default=None, metavar="D,FFN",
                    help="override the layer shape (hidden, ffn); only for quick checks of the JSON contract")
@@ -251,6 +254,29 @@ def profile_loop(args, dev):
     print(json.dumps({"mode": args.mode, "steps": args.steps, "avg_us": e0.elapsed_time(e1) * 1e3 / args.steps, **extra}))
 
 
+def run_generate(args, dev):
+    """Config 4: random-initialised Mixtral-8x7B-architecture decoder, bf16 attention, every expert
+    quantised with mixed bits averaging 2.0; prompt of 512 random tokens, 256 greedy tokens."""
+    import torch
+    from gemq_b200.inference import MixtralDecoder, StaticCache, generate
+    T, new, B = 512, 256, args.batch
+    model = MixtralDecoder(device=dev, seed=1, num_hidden_layers=args.gen_layers)
+    prompt = torch.randint(0, model.config.vocab_size, (B, T), generator=torch.Generator().manual_seed(B)).to(dev)
+    generate(model, prompt, 8, StaticCache(model.config, T + new))  # warm-up (allocations, lazy module loads)
+    seq, stats = generate(model, prompt, new, StaticCache(model.config, T + new))
+    hbm_peak, _, _, kind = peaks()
+    eb, ab = model.expert_bytes_per_token(), model.attention_bytes_per_token(T + new // 2, B)
+    step_s = stats["decode_latency"] / (new - 1)
+    print(json.dumps({
+        "mode": "generate", "workload": "mixtral8x7b_architecture_random_init_greedy_decode (config 4)",
+        "layers": args.gen_layers, "batch": B, "prompt_tokens": T, "new_tokens": new,
+        "prefill_tokens_per_s": stats["prefill_throughput"], "decode_tokens_per_s": stats["decode_throughput"],
+        "decode_ms_per_step": step_s * 1e3,
+        # batch 1: a step streams two experts per layer; larger batches touch most experts (not modelled here)
+        "expert_bytes_per_step_bs1": eb, "attention_and_kv_bytes_per_step": ab,
+        "hbm_frac_bs1": (eb + ab) / step_s / 1e9 / hbm_peak if B == 1 else None, "peak_kind": kind}))
+
+
 def prefill_inputs(T: int):
     import torch
     g = torch.Generator().manual_seed(7)
@@ -354,6 +380,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: gemq_b200 has no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.mode == "generate":
+        run_generate(args, dev)
+        return
     if args.mode != "bench":
         profile_loop(args, dev)
         return
