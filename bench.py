@@ -277,6 +277,42 @@ def run_generate(args, dev):
         "hbm_frac_bs1": (eb + ab) / step_s / 1e9 / hbm_peak if B == 1 else None, "peak_kind": kind}))
 
 
+def run_cfg2(dev):
+    """Config 2: DeepSeek-V2-Lite-shaped layer (hidden 2048, intermediate 1408, 64 experts, top-6, two shared
+    experts at 4 bits), decode batches of 1 and 16 rows.  Bytes: every distinct selected expert once, the
+    shared experts once, the router matrix, at (b + 0.25) / 8 bytes per weight."""
+    import torch
+    from gemq_b200 import synth
+    blk = synth.deepseek_block(seed=0, device=dev)
+    hbm_peak, _, _, kind = peaks()
+    Dd, Fd, SFd, Ed = 2048, 1408, 2816, 64
+    out = {"workload": "deepseek_v2_lite_moe_layer_decode_bs1-16_mixed_bits (config 2)", "peak_kind": kind}
+    for B in (1, 16):
+        xs = [torch.randn(B, 1, Dd, device=dev, generator=torch.Generator(device=dev).manual_seed(10 * B + i)).half()
+              for i in range(8)]
+        byts = []
+        for x in xs:
+            _, _, idx = blk._decode(x.view(B, Dd), 2)
+            distinct = set(idx.view(-1).tolist())
+            byts.append(sum(3 * Dd * Fd * (blk._nbits_host[e] + 0.25) / 8 for e in distinct)
+                        + 3 * Dd * SFd * 4.25 / 8 + 2 * Ed * Dd)
+        for i in range(8):
+            blk(xs[i % 8])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = 64
+        e0.record()
+        for i in range(n):
+            blk(xs[i % 8])
+        e1.record()
+        torch.cuda.synchronize()
+        s = e0.elapsed_time(e1) * 1e-3 / n
+        out[f"bs{B}"] = {"tokens_per_s": B / s, "us_per_step": s * 1e6, "algorithmic_bytes_per_step": sum(byts) / len(byts),
+                         "hbm_frac": sum(byts) / len(byts) / s / 1e9 / hbm_peak,
+                         "path": "one-launch layer kernel per row" if B <= 4 else "expert-sorted grouped GEMM"}
+    return out
+
+
 def prefill_inputs(T: int):
     import torch
     g = torch.Generator().manual_seed(7)
@@ -536,10 +572,12 @@ def main():
     hbm_peak, _, _, peak_kind = peaks()
     achieved = alg / launches_per_step / k_avg_s / 1e9 if fused else None
 
-    prefill = None
+    prefill, cfg2 = None, None
     if not args.no_prefill:
         del graphs, e2e_graphs, kgraph
         prefill = run_prefill(args, rank, local_rank, world, dev)
+        if rank == 0 and world == 1:
+            cfg2 = run_cfg2(dev)
     clocks = sampler.stop(mark0, mark1 + 1)
 
     if rank == 0:
@@ -571,6 +609,8 @@ def main():
             line["cpu_baseline"] = None
         if prefill is not None:
             line["prefill"] = prefill
+        if cfg2 is not None:
+            line["decode_cfg2"] = cfg2
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

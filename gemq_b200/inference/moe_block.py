@@ -25,7 +25,10 @@ from ..kernels._runtime import require_cuda, stream_ptr
 from .packed_linear import is_packed_linear
 
 ROUTE_FP16, ROUTE_FP32_SOFTMAX, ROUTE_FP32 = 0, 1, 2
-_MAX_LOOPED_TOKENS = 16
+# Decode batches up to this many rows run the one-launch layer kernel row by row; larger ones go through the
+# expert-sorted grouped GEMM, which reads every distinct expert (and the shared experts) once per call and is
+# faster from about six rows on (measured on the DeepSeek-V2-Lite shape: 360 vs 275 us at 8 rows, 779 vs 333 at 16).
+_MAX_LOOPED_TOKENS = 4
 
 
 def _excl_cumsum(vals, device):
@@ -367,11 +370,12 @@ class QuantFusedDeepseekV2MoEBlock(_QuantFusedMoEBase):
         fused one-token kernels row by row with this path's fp32 routing."""
         b, s, d = hidden_states.shape
         x = hidden_states.reshape(-1, d)
-        if x.shape[0] <= _MAX_LOOPED_TOKENS:
+        grouped = self._prefill_ok() and x.dtype in (torch.float16, torch.bfloat16)
+        if x.shape[0] <= _MAX_LOOPED_TOKENS or (not grouped and x.shape[0] <= 16):
             xh = x if x.dtype == torch.float16 else x.to(torch.float16)
             out, _, _ = self._decode(xh.contiguous(), ROUTE_FP32)
             return out.to(hidden_states.dtype).reshape(b, s, d)
-        if self._prefill_ok() and x.dtype in (torch.float16, torch.bfloat16):
+        if grouped:
             out, _, _, _ = self._prefill(x, ROUTE_FP32, bool(self.norm_topk_prob))
             return out.reshape(b, s, d)
         raise self._unsupported(x)
