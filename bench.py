@@ -31,10 +31,10 @@ WORKLOAD = "mixtral8x7b_moe_layer_decode_bs1_mixed_1-4bit_g128 (config 1)"
 PREFILL_WORKLOAD = "mixtral8x7b_moe_layer_prefill_4096tok_top2_dirichlet0.5_mixed_bits (config 3)"
 LAYER_SEED0 = 100
 # DRAM bytes (read + write) of one launch of the decode layer kernel over its algorithmic bytes,
-# from an ncu capture of three launches; applied to the bench's own average bytes per launch.
-DECODE_TRAFFIC_RATIO = 1.02
+# from an ncu capture of three launches (1.038, 1.035, 1.012); applied to the bench's own average bytes per launch.
+DECODE_TRAFFIC_RATIO = 1.03
 # DRAM bytes of one prefill call at N = 1 (gate/up launch + down launch), from an ncu capture.
-PREFILL_TRAFFIC_BYTES = 489.2e6 + 220.7e6 + 465.9e6 + 58.8e6
+PREFILL_TRAFFIC_BYTES = 497.4e6 + 218.5e6 + 464.7e6 + 55.2e6
 MIN_TIMED_SECONDS = 0.5
 
 
