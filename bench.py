@@ -381,13 +381,15 @@ def run_prefill(args, rank, local_rank, world, dev):
     if placement is None:
         share = 1.0
     else:
-        per_rank = [sum(rows[e] for e in range(E) if placement[e] == r) for r in range(world)]
+        per_rank = [sum(rows[e] * sh for e, r, sh in placement if r == k) for k in range(world)]
         share = max(per_rank) / float(sum(rows))
     rec = {"metric": "moe_layer_prefill_tokens_per_s", "value": T * steps / (ms * 1e-3), "unit": "tokens/s",
            "steps": steps, "warmup": warm, "ms_per_step": ms / steps, "scaling": "strong", "dtype": "f16",
            "config": {"workload": PREFILL_WORKLOAD, "tokens": T, "bits": bits, "tokens_per_rank": hi - lo,
                       "parallelism": f"expert-parallel x{world}" if world > 1 else "one GPU",
-                      "routed_rows_per_expert": rows, "expert_to_rank": placement,
+                      "routed_rows_per_expert": rows,
+                      # [expert, rank, share of the expert's rows]: an expert above a rank's fair share has replicas
+                      "expert_rank_share": [[e, r, round(sh, 4)] for e, r, sh in placement] if placement else None,
                       # share of the routed rows on the busiest rank (1/world = perfectly even): the ceiling of
                       # the speed-up over one GPU is 1 / share
                       "busiest_rank_row_share": share,

@@ -64,6 +64,11 @@ _SIGNATURES = {
     "gemq_moe_prefill_scratch_bytes": (_Z, [C.POINTER(MoeLayer), _I]),
     "gemq_moe_prefill": (_I, [C.POINTER(MoeLayer), _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P]),
     "gemq_moe_prefill_error_word": (_P, [C.POINTER(MoeLayer), _I, _P]),
+    "gemq_ep_plan_scratch_bytes": (_Z, [_I]),
+    "gemq_ep_plan": (_I, [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _Z, _P]),
+    "gemq_ep_pack_rows": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "gemq_ep_unpack_rows": (_I, [_P, _I, _I, _P, _P, _P, _P]),
+    "gemq_ep_combine": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P]),
     "gemq_dequant_gemv_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "gemq_static_scratch_bytes": (_Z, []),
     "gemq_workspace_error_word": (_P, [_P]),

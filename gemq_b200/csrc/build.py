@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libgemq_b200.so")
-SOURCES = ["pack.cu", "tma.cu", "gemv.cu", "gemv_stream.cu", "route.cu", "layer.cu", "decode_fused.cu", "gemm_sm100.cu", "no_alloc.cu"]
+SOURCES = ["pack.cu", "tma.cu", "gemv.cu", "gemv_stream.cu", "route.cu", "layer.cu", "decode_fused.cu", "gemm_sm100.cu", "expert_parallel.cu", "no_alloc.cu"]
 HEADERS = ["common.cuh", "gemv.cuh", "ptx.cuh", os.path.join(ROOT, "include", "gemq_b200.h")]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -68,18 +68,27 @@ def deepseek_block(seed: int = 0, device="cuda", bits=None, shared_bits: int = 4
 
 
 def mixtral_expert_parallel(rank: int, world: int, seed: int = 0, device="cuda", bits=None, group: int = 128,
-                            process_group=None, routed_rows=None, **overrides):
+                            process_group=None, routed_rows=None, replicate=True, placement=None, **overrides):
     """This rank's shard of a Mixtral-shaped layer.  Without ``routed_rows`` rank r holds experts
     ``[r*E/world, (r+1)*E/world)``; with it (rows each expert receives, e.g. from calibration) the
-    experts are placed so that the rows per rank even out.  Every expert is drawn from its own
-    seed, so all ranks agree on the full layer.  Returns (layer, bits, expert -> rank list)."""
-    from .inference.expert_parallel import ExpertParallelMixtralMoE, balanced_placement, contiguous_placement
+    experts are placed so that the rows per rank even out, an expert above a rank's fair share
+    being held by several ranks when ``replicate``.  Every expert is drawn from its own seed, so
+    all ranks agree on the full layer.  ``placement`` gives the table directly.  Returns (layer, bits, [(expert, rank, share), ...])."""
+    from .inference.expert_parallel import (ExpertParallelMixtralMoE, Placement, balanced_placement, contiguous_placement,
+                                            replicated_placement)
     cfg = {**MIXTRAL_8X7B, **overrides}
     E, D, Fd, A = cfg["num_local_experts"], cfg["hidden_size"], cfg["intermediate_size"], cfg["num_experts_per_tok"]
     bits = bits or draw_expert_bits(E, seed)
     gate = (torch.randn(E, D, device=device, generator=generator(seed, device)) * 0.02).to(torch.float16)
-    place = balanced_placement(routed_rows, world) if routed_rows is not None else contiguous_placement(E, world)
-    mine = [e for e in range(E) if int(place[e]) == rank]
+    if placement is not None:
+        place = placement
+    elif routed_rows is None:
+        place = Placement.from_expert_to_rank(contiguous_placement(E, world), world)
+    elif replicate:
+        place = replicated_placement(routed_rows, world)
+    else:
+        place = Placement.from_expert_to_rank(balanced_placement(routed_rows, world), world)
+    mine = place.experts_of[rank]
     w1, w2, w3 = [], [], []
     for e in mine:
         gen = generator(seed * 1000 + 17 * e + 1, device)
@@ -91,4 +100,4 @@ def mixtral_expert_parallel(rank: int, world: int, seed: int = 0, device="cuda",
         local_cfg = SimpleNamespace(hidden_size=D, intermediate_size=Fd, num_local_experts=len(mine), num_experts_per_tok=1)
         local = QuantFusedMixtralMoEBlock.from_linears(local_cfg, gate[mine].clone(), w1, w2, w3)
     layer = ExpertParallelMixtralMoE(local, gate, E, A, process_group, expert_to_rank=place)
-    return layer, bits, place.tolist()
+    return layer, bits, [list(i) for i in place.instances]

@@ -219,6 +219,44 @@ int gemq_moe_prefill(const gemq_moe_layer_t* layer, const void* x, void* out, in
 /* Device address of the error word gemq_moe_prefill writes in `scratch` (0 = every wait was met). */
 const int32_t* gemq_moe_prefill_error_word(const gemq_moe_layer_t* layer, int tokens, void* scratch);
 
+/* ---- expert-parallel prefill: the token exchange around the local grouped GEMM ---------------- */
+
+/* No counterpart in the reference (its n-token forward, gemq/inference/moe_block.py:165-198,
+ * loops over the experts of one GPU).  With the experts spread over `world` ranks these four
+ * calls are the device side of the all-to-all form of that loop; the collectives themselves are
+ * the caller's (NCCL).  A placement table says where expert e lives: replica j (j < replicas) on
+ * rank rank_tab[e*replicas + j], at position local_tab[e*replicas + j] among that rank's experts,
+ * taking the sender's rows of e whose position, as a fraction of the sender's rows of e, is below
+ * upper_tab[e*replicas + j] and not below the previous replica's bound (unused replicas: 2.0).
+ *
+ * gemq_ep_plan: sel int64 [pairs] (= [tokens, top_k] flattened) ->
+ *   order int64 [pairs]       pair indices sorted by (destination rank, expert), ties by pair index
+ *   loc_sorted int32 [pairs]  position of the pair's expert on its destination, in that order
+ *   where int64 [pairs]       inverse permutation: row of pair i in the sorted order
+ *   send_counts int64 [world] pairs per destination
+ * One launch, no host read.  scratch: gemq_ep_plan_scratch_bytes(pairs), zero-filled once; its
+ * first int32 receives a non-zero code when an id lies outside [0, n_experts) (the id is clamped). */
+size_t gemq_ep_plan_scratch_bytes(int pairs);
+int gemq_ep_plan(const int64_t* sel, int pairs, int n_experts, int world, int replicas, const int32_t* rank_tab,
+                 const int32_t* local_tab, const float* upper_tab, int64_t* order, int32_t* loc_sorted, int64_t* where,
+                 int64_t* send_counts, void* scratch, size_t scratch_bytes, gemq_stream_t stream);
+
+/* payload [pairs, D + 8] (16-bit elements): row p = the token row of pair order[p], then the
+ * int32 loc_sorted[p], the pair's 16-bit routing weight and zero padding.  D % 8 == 0. */
+int gemq_ep_pack_rows(const void* x, const int64_t* order, const int32_t* loc_sorted, const void* weights, int pairs,
+                      int top_k, int D, void* payload, gemq_stream_t stream);
+
+/* The inverse on the receiving rank: payload [rows, D + 8] -> x [rows, D], expert int64 [rows],
+ * weights 16-bit [rows]. */
+int gemq_ep_unpack_rows(const void* payload, int rows, int D, void* x, int64_t* expert, void* weights,
+                        gemq_stream_t stream);
+
+/* out [tokens, D] = the token's top_k returned rows back[where[token*top_k + slot]] added in
+ * increasing expert id (ties by slot), rounded to the activation type after every addition: the
+ * index_add_ order of gemq/inference/moe_block.py:191-195. */
+int gemq_ep_combine(const void* back, const int64_t* where, const int64_t* sel, int tokens, int top_k, int D,
+                    int is_bf16, void* out, gemq_stream_t stream);
+
 /* ---- for callers that cannot allocate --------------------------------------------------------- */
 
 /* No counterpart in the reference.  y[1, N] = x[1, K] @ deq(wq), the same result as

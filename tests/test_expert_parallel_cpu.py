@@ -7,8 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from gemq_b200.inference.expert_parallel import (balanced_placement, combine_in_expert_order, dispatch_plan,
-                                                 expert_parallel_forward, local_ids)
+from gemq_b200.inference.expert_parallel import (Placement, balanced_placement, combine_in_expert_order, dispatch_plan,
+                                                 expert_parallel_forward, local_ids, placed_plan, replicated_placement)
 
 E, A, D = 8, 2, 16
 
@@ -67,12 +67,36 @@ def test_dispatch_plan_with_placement_groups_by_rank():
     assert sorted(order.tolist()) == list(range(29 * A))
 
 
+def test_replicated_placement_splits_the_hot_expert():
+    rows = [631, 37, 99, 707, 1509, 1600, 3414, 195]  # one expert draws 42 % of the rows
+    for world in (2, 4, 8):
+        place = replicated_placement(rows, world)
+        load = place.rows_per_rank(rows)
+        assert abs(sum(load) - sum(rows)) < 1e-6
+        assert max(load) / sum(rows) < 1.1 / world          # without replicas: 0.42 at four ranks
+        for e in range(8):
+            assert abs(sum(s for e2, _, s in place.instances if e2 == e) - 1.0) < 1e-9
+        assert [list(i) for i in place.instances] == [list(i) for i in replicated_placement(rows, world).instances]
+    place = replicated_placement(rows, 4)
+    assert sorted(r for e, r, _ in place.instances if e == 6) == [0, 1]
+    # a sender's rows of the split expert go to the replicas in the placement's proportions, in order
+    sel = torch.tensor([[6, 0]] * 10)
+    order, counts, loc = placed_plan(sel, place)
+    flat = sel.reshape(-1)[order]
+    assert counts.tolist() == [6, 4, 0, 10] and flat.tolist() == [6] * 10 + [0] * 10
+    assert order[:10].tolist() == [2 * i for i in range(10)]
+
+
 def _worker(rank, world, port, results, placement=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    place = torch.tensor(placement) if placement is not None else torch.arange(E) // (E // world)
-    mine = [e for e in range(E) if int(place[e]) == rank]
+    if isinstance(placement, list) and isinstance(placement[0], tuple):
+        place = Placement(placement, E, world)
+        mine = place.experts_of[rank]
+    else:
+        place = torch.tensor(placement) if placement is not None else torch.arange(E) // (E // world)
+        mine = [e for e in range(E) if int(place[e]) == rank]
     T = 11 + 3 * rank  # ragged token counts per rank
     x, w, sel = make_inputs(100 + rank, T)
 
@@ -106,6 +130,18 @@ def test_expert_parallel_with_uneven_placement_gloo():
     results = mgr.dict()
     port = 31500 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(world, port, results, [1, 0, 1, 1, 0, 1, 1, 1]), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}
+
+
+def test_expert_parallel_with_replicated_experts_gloo():
+    """Experts 0 and 5 live on both ranks; each sender splits its rows between the replicas."""
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 33500 + (os.getpid() % 2000)
+    inst = [(0, 0, 0.3), (0, 1, 0.7), (1, 0, 1.0), (2, 1, 1.0), (3, 1, 1.0), (4, 0, 1.0), (5, 1, 0.5), (5, 0, 0.5),
+            (6, 0, 1.0), (7, 1, 1.0)]
+    mp.spawn(_worker, args=(world, port, results, inst), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
 
 

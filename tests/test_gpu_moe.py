@@ -206,7 +206,11 @@ def _ep_worker(rank, world, port, results):
     # experts placed by (made-up) routed-row statistics: rank 0 holds expert 0 alone, rank 1 the other three
     ep, _, place = synth.mixtral_expert_parallel(rank, world, seed=5, device=dev, bits=bits, routed_rows=[90, 40, 30, 20],
                                                  **dims)
-    assert place == [0, 1, 1, 1]
+    assert place == [[0, 0, 1.0], [1, 1, 1.0], [2, 1, 1.0], [3, 1, 1.0]]
+    # the same layer with expert 0 held by both ranks (60 % / 40 % of its rows) and expert 2 moved to rank 0
+    from gemq_b200.inference.expert_parallel import Placement
+    split = Placement([(0, 0, 0.6), (0, 1, 0.4), (1, 1, 1.0), (2, 0, 1.0), (3, 1, 1.0)], 4, world)
+    ep2, _, _ = synth.mixtral_expert_parallel(rank, world, seed=5, device=dev, bits=bits, placement=split, **dims)
     full, _, _ = synth.mixtral_expert_parallel(0, 1, seed=5, device=dev, bits=bits, **dims)  # all experts, no exchange
     g = torch.Generator().manual_seed(11 + rank)
     T = 150 + 20 * rank
@@ -219,7 +223,8 @@ def _ep_worker(rank, world, port, results):
     rows = x.repeat_interleave(2, 0)
     yy = full.local._prefill(rows, 1, True, routing=(w.reshape(-1, 1), sel.reshape(-1, 1)))[0]
     ref = combine_in_expert_order(yy.view(T, 2, -1), sel)
-    results[rank] = float((y.float() - ref.float()).abs().max())
+    y2 = ep2.forward_routed(x, w, sel)
+    results[rank] = max(float((y.float() - ref.float()).abs().max()), float((y2.float() - ref.float()).abs().max()))
     dist.barrier()
     dist.destroy_process_group()
 
