@@ -91,6 +91,7 @@ struct FusedParams {
   float* h;              // [A*F + SF]
   int c_total;           // columns of a partial row: gate/up columns of all slots, then the down columns
   int up_cols;
+  long long wq_bytes[3]; // extent of the stacked gate / up / down code tensors (0: unknown)
 };
 
 struct SlotInfo {
@@ -208,19 +209,19 @@ __device__ __forceinline__ int scale_exp_b3(float mx) {
 // round(x * f) + 0x8080 in the low mantissa bits: bytes 0, 1 = low balanced digits + 128, byte 2 = top digit + 64
 __device__ __forceinline__ uint32_t digits_word(float x, float f) { return __float_as_uint(fmaf(x, f, 12615808.0f)); }
 
-// Wait until the h chunks (= reduction groups of phase 1) [g0, g1) of a slot are complete.  Lane 0
-// polls; the flags are written by the finisher that completed the chunk, after a fence.
+// Wait until the h chunks (= reduction groups of phase 1) [g0, g1) of a slot are complete.  The
+// flags are written by the finisher that completed the chunk, after a fence.  Every lane polls a
+// flag of its own, so the wait costs one L2 round trip however many chunks it covers.
+__device__ __forceinline__ void poll_flag(const int* flag, int* err, int spin) {
+  int i = 0;
+  while (ld_acquire(flag) == 0) {
+    if (++i > spin) { atomicExch(err, kErrPhase); break; }
+    __nanosleep(32);
+  }
+}
 __device__ __forceinline__ void wait_groups(const int* flags, int g0, int g1, int* err, int spin) {
   if (flags) {
-    if ((threadIdx.x & 31) == 0) {
-      for (int gq = g0; gq < g1; ++gq) {
-        int i = 0;
-        while (ld_acquire(flags + gq) == 0) {
-          if (++i > spin) { atomicExch(err, kErrPhase); break; }
-          __nanosleep(32);
-        }
-      }
-    }
+    for (int gq = g0 + static_cast<int>(threadIdx.x & 31); gq < g1; gq += 32) poll_flag(flags + gq, err, spin);
     __syncwarp();
   }
 }
@@ -329,17 +330,21 @@ __device__ __forceinline__ void build_b3(Tables& T, const void* x, bool xf32, in
   __half* tab1 = reinterpret_cast<__half*>(tab1w);
   int taken = 0, gq = 0;
   while (gq < ngroups) {
-    int mine[4], nmine = 0;
+    int mine[4] = {0, 0, 0, 0}, nmine = 0;
     for (; gq < ngroups && nmine < 4; ++gq) {
       if (gq / 5 < 32 && !((need >> (gq / 5)) & 1u)) continue;
       if ((taken++ % kCons) != warp) continue;
       mine[nmine++] = gq;
     }
     float xv[4][4];
+    if (flags) {  // lanes 0..3 poll the flags of the four groups together
+      const int gm = lane == 0 ? mine[0] : (lane == 1 ? mine[1] : (lane == 2 ? mine[2] : mine[3]));
+      if (lane < nmine) poll_flag(flags + gm, err, spin);
+      __syncwarp();
+    }
 #pragma unroll
     for (int u = 0; u < 4; ++u)
       if (u < nmine) {
-        wait_groups(flags, mine[u], mine[u] + 1, err, spin);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const size_t k = static_cast<size_t>(mine[u]) * kGroup + i * 32 + lane;
@@ -409,28 +414,54 @@ __device__ void route_cta(Smem& S, const FusedParams& P) {
   parts = parts > 8 ? 8 : parts;
   while (parts > 1 && (D % (parts * 256)) != 0) parts >>= 1;
   const int seg = D / parts;
-  for (int task = warp; task < E * parts; task += kWarps) {
-    const int e = task / parts, sg = task - e * parts;
-    const __half* ge = P.gate + static_cast<size_t>(e) * D + static_cast<size_t>(sg) * seg;
-    const __half* xs = P.x + static_cast<size_t>(sg) * seg;
-    float s = 0.f;
+  // Two (expert, segment) tasks per pass, the loads of both in flight together; each task keeps its
+  // own summation order, so the logits do not depend on how the tasks are batched.  Every CTA
+  // reads the whole router matrix: the CTAs start at different tasks so that at any moment they
+  // pull different lines out of L2 instead of all queueing at the same slices.
+  const int rot = static_cast<int>(blockIdx.x % static_cast<unsigned>(E * parts));
+#pragma unroll 1
+  for (int task0 = warp; task0 < E * parts; task0 += 2 * kWarps) {
+    float acc[2] = {0.f, 0.f};
+#pragma unroll 1
     for (int k0 = 0; k0 < seg; k0 += 4 * 256) {
-      uint4 gq[4], xq[4];
+      uint4 gq[2][4], xq[2][4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k = k0 + (i * 32 + lane) * 8;
-        if (k < seg) {
-          gq[i] = *reinterpret_cast<const uint4*>(ge + k);
-          xq[i] = *reinterpret_cast<const uint4*>(xs + k);
+      for (int u = 0; u < 2; ++u) {
+        if (task0 + u * kWarps < E * parts) {
+          const int task = (task0 + u * kWarps + rot) % (E * parts);
+          const int e = task / parts, sg = task - e * parts;
+          const __half* ge = P.gate + static_cast<size_t>(e) * D + static_cast<size_t>(sg) * seg;
+          const __half* xs = P.x + static_cast<size_t>(sg) * seg;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int k = k0 + (i * 32 + lane) * 8;
+            if (k < seg) {
+              gq[u][i] = *reinterpret_cast<const uint4*>(ge + k);
+              xq[u][i] = *reinterpret_cast<const uint4*>(xs + k);
+            }
+          }
         }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        if (k0 + (i * 32 + lane) * 8 < seg) s += dot8h(xq[i], gq[i]);
+      for (int u = 0; u < 2; ++u) {
+        if (task0 + u * kWarps < E * parts) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (k0 + (i * 32 + lane) * 8 < seg) acc[u] += dot8h(xq[u][i], gq[u][i]);
+        }
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) S.part_sum[e][sg] = s;
+    for (int u = 0; u < 2; ++u) {
+      if (task0 + u * kWarps < E * parts) {
+        const int task = (task0 + u * kWarps + rot) % (E * parts);
+        const int e = task / parts, sg = task - e * parts;
+        float s = acc[u];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) S.part_sum[e][sg] = s;
+      }
+    }
   }
   __syncthreads();
   if (threadIdx.x < E) {
@@ -454,6 +485,7 @@ __device__ void route_cta(Smem& S, const FusedParams& P) {
   if (lane >= E) p = -1.f;
   float my_w = 0.f;
   int my_i = 0;
+#pragma unroll 1
   for (int a = 0; a < A; ++a) {
     float bv = p > -2.f ? p : -2.f;
     int bi = p > -2.f ? lane : 0x7fffffff;
@@ -481,6 +513,16 @@ __device__ void route_cta(Smem& S, const FusedParams& P) {
 }
 
 // ---- plan (warp 0) ----------------------------------------------------------------------------
+// a / b for a < 2^24, b > 0: one approximate reciprocal and a correction instead of the integer
+// division sequence (the plan is a single warp's chain of dependent instructions).
+__device__ __forceinline__ unsigned small_div(unsigned a, unsigned b) {
+  unsigned q = __float2uint_rz(__fdividef(__uint2float_rz(a), __uint2float_rz(b)));
+  if (q * b > a) --q;
+  if ((q + 1) * b <= a) ++q;
+  return q;
+}
+__device__ __forceinline__ int quanta_of(int groups, int bits) { return bits == 3 ? (groups + 4) / 5 : (groups + 3) >> 2; }
+
 __device__ void make_plan(Smem& S, const FusedParams& P) {
   const int lane = threadIdx.x & 31;
   const int Sn = P.S;
@@ -519,8 +561,8 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
     }
     I.bits[0] = b1; I.bits[1] = b2;
     I.F = Fs;
-    I.nq[0] = cdiv(P.D / kGroup, quantum_groups(b1));
-    I.nq[1] = cdiv(Fs / kGroup, quantum_groups(b2));
+    I.nq[0] = quanta_of(P.D / kGroup, b1);
+    I.nq[1] = quanta_of(Fs / kGroup, b2);
     I.nch[0] = cdiv(Fs, 128);
     I.nch[1] = cdiv(P.D, 128);
     S.slot[lane] = I;
@@ -528,7 +570,7 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
   // exclusive prefix sums over the slots: h / partial offsets, pair counters, down quanta
   int nch0 = lane < Sn ? cdiv(Fs, 128) : 0;
   int fs = lane < Sn ? Fs : 0;
-  int nq1 = lane < Sn ? cdiv(Fs / kGroup, quantum_groups(b2)) : 0;
+  int nq1 = lane < Sn ? quanta_of(Fs / kGroup, b2) : 0;
   int in_nch = nch0, in_fs = fs, in_nq1 = nq1;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -557,6 +599,7 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
   __syncwarp();
   // ranges and parts of the two phases
   int pbase = 0;
+#pragma unroll 1
   for (int ph = 0; ph < 2; ++ph) {
     unsigned n_units = 0, cost = 1;
     int nq = 1;
@@ -573,15 +616,20 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
       const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += t;
     }
-    const unsigned long long total = __shfl_sync(0xffffffffu, incl, 31);
+    const unsigned total = __shfl_sync(0xffffffffu, incl, 31);
     const unsigned prefix = incl - wgt;
-    const unsigned lo = static_cast<unsigned>(total * blockIdx.x / gridDim.x);
-    const unsigned hi = static_cast<unsigned>(total * (blockIdx.x + 1) / gridDim.x);
-    unsigned ulo = lo <= prefix ? 0u : (lo - prefix + cost - 1) / cost;
-    unsigned uhi = hi <= prefix ? 0u : (hi - prefix + cost - 1) / cost;
+    // cut points: any monotone function of the CTA index evaluated the same way by both neighbours
+    const float per_cta = static_cast<float>(total) / static_cast<float>(gridDim.x);
+    const unsigned lo = blockIdx.x == 0 ? 0u : min(total, static_cast<unsigned>(per_cta * static_cast<float>(blockIdx.x)));
+    const unsigned hi = blockIdx.x + 1 == gridDim.x ? total
+                                                    : min(total, static_cast<unsigned>(per_cta * static_cast<float>(blockIdx.x + 1)));
+    const bool small = total < (1u << 23);  // always, for the layers this kernel takes; the exact form stays as the guard
+    unsigned ulo = lo <= prefix ? 0u : (small ? small_div(lo - prefix + cost - 1, cost) : (lo - prefix + cost - 1) / cost);
+    unsigned uhi = hi <= prefix ? 0u : (small ? small_div(hi - prefix + cost - 1, cost) : (hi - prefix + cost - 1) / cost);
     ulo = min(ulo, n_units);
     uhi = min(uhi, n_units);
-    const int np = uhi > ulo ? static_cast<int>((uhi - 1) / nq - ulo / nq + 1) : 0;
+    const unsigned cm_lo = small ? small_div(ulo, nq) : ulo / nq;
+    const int np = uhi > ulo ? static_cast<int>((small ? small_div(uhi - 1, nq) : (uhi - 1) / nq) - cm_lo + 1) : 0;
     int inp = np;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -597,7 +645,8 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
       const int B = I.bits[ph];
       const int K = ph ? I.F : P.D, N = ph ? P.D : I.F;
       const int ngroups = K / kGroup;
-      const int first_cm = static_cast<int>(ulo) / nq;
+      const int first_cm = static_cast<int>(cm_lo);
+#pragma unroll 1
       for (int k = 0; k < np; ++k, ++pi) {
         const int cm = first_cm + k;
         const int c = ph ? cm : (cm >> 1), m = ph ? 0 : (cm & 1), mi = ph ? 2 : m;
@@ -609,7 +658,7 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
         d.sc = I.sc[mi] + n0;
         d.zr = I.zr[mi] + n0;
         d.N = N; d.B = B; d.ngroups = ngroups;
-        d.kw = B == 3 ? b3_rows(K) : K / (32 / B);
+        d.kw = B == 3 ? b3_rows(K) : (K * B) >> 5;
         if (B == 3) { d.run_lo = qa; d.run_hi = min(qb, nq); }
         else { d.run_lo = 2 * qa; d.run_hi = min(2 * qb, cdiv(ngroups, 2)); }
         d.ncols = min(128, N - n0);
@@ -996,9 +1045,12 @@ __device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zer
 #pragma unroll
   for (int r = 0; r < 4; ++r) L.roff[r] = ring_off(r, lane);
   loader_next_run(&L, &S, kq, lane, 1);
-  // the weights do not depend on the tables: fill the ring first
+  // The weights do not depend on the tables: start filling the ring first.  Only part of it:
+  // the copies queue up behind the memory system's limit on requests in flight, and the first
+  // table should be built while they travel, not after the last one was accepted.
+  constexpr int kEarly = 2;
 #pragma unroll 1
-  for (int k = 0; k < kRing - 1; ++k) loader_step(L, S, kq, lane);
+  for (int k = 0; k < kEarly; ++k) loader_step(L, S, kq, lane);
   Cursor C;
   C.ring = S.ring[warp][0];
   C.slot = 0;
@@ -1030,6 +1082,10 @@ __device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zer
       // the h chunks of a slot are the reduction groups of its down projection: their flags gate the build
       const int* flags = d.phase ? P.counters + 2 * S.pairs_total + S.slot[d.s].ctrb : nullptr;
       build_table(&S.T, xsrc, d.phase, d.ngroups * kGroup, B, need, flags, err, S.spin, warp, lane);
+      if (cur_tab < 0) {
+#pragma unroll 1
+        for (int k = kEarly; k < kRing - 1; ++k) loader_step(L, S, kq, lane);
+      }
       cur_tab = d.tab;
     }
     if (B == 1) part_i8<1>(R, L, C, S, d, kq, lane);
@@ -1109,29 +1165,39 @@ __device__ __noinline__ float4 drain_slots(float* src, size_t c_total, const uns
   return sum;
 }
 
-// Two jobs at once (gate and up partials of a column chunk), slot sets given by value: the
-// loads of both jobs are in flight together; each job is summed in slice order.
+// Two jobs at once (gate and up partials of a column chunk), slot sets given by value: up to
+// four slots of each job are in flight together (one L2 round trip for a strip cut in up to four);
+// each job is summed in slice order.
 __device__ __forceinline__ void drain_pair(float* sa, float* sb, size_t c_total, unsigned ma, unsigned mb, float4& a,
                                            float4& b) {
+  constexpr int kB = 4;
   a = make_float4(0.f, 0.f, 0.f, 0.f);
   b = a;
   const float4 zero = a;
   while (ma | mb) {
-    float4* qa = nullptr;
-    float4* qb = nullptr;
-    float4 ta = zero, tb = zero;
-    if (ma) {
-      qa = reinterpret_cast<float4*>(sa + static_cast<size_t>(__ffs(ma) - 1) * c_total);
-      ma &= ma - 1;
-      ta = __ldcg(qa);
+    float4* qa[kB];
+    float4* qb[kB];
+    float4 ta[kB], tb[kB];
+#pragma unroll
+    for (int i = 0; i < kB; ++i) {
+      qa[i] = nullptr;
+      qb[i] = nullptr;
+      if (ma) {
+        qa[i] = reinterpret_cast<float4*>(sa + static_cast<size_t>(__ffs(ma) - 1) * c_total);
+        ma &= ma - 1;
+        ta[i] = __ldcg(qa[i]);
+      }
+      if (mb) {
+        qb[i] = reinterpret_cast<float4*>(sb + static_cast<size_t>(__ffs(mb) - 1) * c_total);
+        mb &= mb - 1;
+        tb[i] = __ldcg(qb[i]);
+      }
     }
-    if (mb) {
-      qb = reinterpret_cast<float4*>(sb + static_cast<size_t>(__ffs(mb) - 1) * c_total);
-      mb &= mb - 1;
-      tb = __ldcg(qb);
+#pragma unroll
+    for (int i = 0; i < kB; ++i) {
+      if (qa[i]) { a.x += ta[i].x; a.y += ta[i].y; a.z += ta[i].z; a.w += ta[i].w; __stcg(qa[i], zero); }
+      if (qb[i]) { b.x += tb[i].x; b.y += tb[i].y; b.z += tb[i].z; b.w += tb[i].w; __stcg(qb[i], zero); }
     }
-    if (qa) { a.x += ta.x; a.y += ta.y; a.z += ta.z; a.w += ta.w; __stcg(qa, zero); }
-    if (qb) { b.x += tb.x; b.y += tb.y; b.z += tb.z; b.w += tb.w; __stcg(qb, zero); }
   }
 }
 
@@ -1310,6 +1376,22 @@ __global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_co
     for (size_t i = threadIdx.x; i < lines; i += kThreads)
       asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(P.gate) + i * 128));
   }
+  // the activation's lines too: whoever writes them later writes into L2, where they then already are
+  for (size_t i = threadIdx.x; i < (static_cast<size_t>(P.D) * sizeof(__half) + 127) / 128; i += kThreads)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(P.x) + i * 128));
+  // One line of every 2 MB page of the expert matrices: the address translations are resolved
+  // while the previous kernel drains, not when all CTAs ask for their first rows at once.
+  {
+    constexpr long long kPage = 2ll << 20;
+    const char* base[3] = {reinterpret_cast<const char*>(P.w1.wq), reinterpret_cast<const char*>(P.w3.wq),
+                           reinterpret_cast<const char*>(P.w2.wq)};
+#pragma unroll
+    for (int m = 0; m < 3; ++m) {
+      const long long pages = (P.wq_bytes[m] + kPage - 1) / kPage;
+      for (long long i = blockIdx.x * kThreads + threadIdx.x; i < pages; i += static_cast<long long>(gridDim.x) * kThreads)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base[m] + i * kPage));
+    }
+  }
   // The next kernel of the stream may start its prologue; everything below reads results of
   // the previous kernel (the activation, the zeroed workspace) and therefore waits for it.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -1328,7 +1410,6 @@ __global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_co
   if (warp == 0) make_plan(S, P);
   __syncthreads();
   if (S.overflow && threadIdx.x == 0) atomicExch(err, 14);
-  __syncthreads();
   if (warp < kCons) consumer_role(S, P, zero_row, err);
   else finisher_role(S, P, err);
   __syncthreads();
@@ -1427,6 +1508,9 @@ int launch_decode_fused(const gemq_moe_layer_t* L, const __half* x, __half* out,
     P.sbits = L->s1.nbits;
   }
   P.partial = partial; P.counters = counters; P.h = h;
+  P.wq_bytes[0] = L->w1.wq_rows * static_cast<long long>(P.F) * 4;
+  P.wq_bytes[1] = L->w3.wq_rows * static_cast<long long>(P.F) * 4;
+  P.wq_bytes[2] = L->w2.wq_rows * static_cast<long long>(P.D) * 4;
   const int up_cols = 2 * (P.A * P.F + P.SF), down_cols = P.S * P.D;
   P.c_total = up_cols + down_cols;
   P.up_cols = up_cols;
