@@ -61,7 +61,10 @@ constexpr int kExitSlot = kMaxCounters - 3;  // CTAs that left this launch
 // words of activation tables: three digit planes of kMaxK bytes (+ padding), or the 3-bit
 // tables (16 halves per packed row + 16 per group for the rows that straddle two groups)
 constexpr int kTabWordsI8 = 3 * (kMaxK / 4 + 16);
-constexpr int kTabWordsB3 = ((kMaxK + 9) / 10) * 8 + 8 + kMaxGroups * 8;
+// 3-bit: per digit plane two words per packed row (rows rounded up to whole 64-row runs) and one
+// word per pair of rows, plus the pads that spread the planes over the banks
+constexpr int kB3RowsMax = (((kMaxK + 9) / 10 + 63) / 64) * 64;
+constexpr int kTabWordsB3 = 3 * (2 * kB3RowsMax + 8) + 3 * (kB3RowsMax / 2 + 4);
 constexpr int kTabWords = kTabWordsI8 > kTabWordsB3 ? kTabWordsI8 : kTabWordsB3;
 
 enum { kErrBadExpert = 7, kErrRedFull = 11, kErrRedEmpty = 12, kErrPhase = 13 };
@@ -144,6 +147,7 @@ struct Smem {
 };
 
 static_assert(sizeof(Smem) <= 227 * 1024 - 64, "shared memory of the layer kernel exceeds the per-CTA limit");
+static_assert(kMaxGroups <= 32 * kCons, "the 3-bit table builder deals a warp at most one group per lane");
 
 // ---- small helpers ----------------------------------------------------------------------
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -165,7 +169,7 @@ __device__ __forceinline__ int quantum_groups(int bits) { return bits == 3 ? 5 :
 // (relative time of a quantum measured in place: the low bit widths are bound by the MMA and
 // logic issue rate, not by their bytes)
 __device__ __forceinline__ unsigned quantum_cost(int bits) {
-  return bits == 1 ? 32u : (bits == 2 ? 36u : (bits == 3 ? 98u : 49u));
+  return bits == 1 ? 32u : (bits == 2 ? 36u : (bits == 3 ? 74u : 49u));
 }
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -175,16 +179,6 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_f16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                        uint32_t b1) {
-  float f0 = __int_as_float(d[0]), f1 = __int_as_float(d[1]), f2 = __int_as_float(d[2]), f3 = __int_as_float(d[3]);
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(f0), "+f"(f1), "+f"(f2), "+f"(f3)
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  d[0] = __float_as_int(f0); d[1] = __float_as_int(f1); d[2] = __float_as_int(f2); d[3] = __float_as_int(f3);
-}
-
 // ---- integer operand format (1/2/4-bit) ---------------------------------------------------
 template <int B>
 struct I8 {
@@ -200,11 +194,6 @@ struct I8 {
 __device__ __forceinline__ int scale_exp_i8(float mx) {
   int c = 20 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
   return c < -60 ? -60 : (c > 60 ? 60 : c);
-}
-// c = 14 - floor(log2(max|x|)) (3-bit: fp16 operands).
-__device__ __forceinline__ int scale_exp_b3(float mx) {
-  int c = 14 - (static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu) - 127);
-  return c < -15 ? -15 : (c > 40 ? 40 : c);
 }
 // round(x * f) + 0x8080 in the low mantissa bits: bytes 0, 1 = low balanced digits + 128, byte 2 = top digit + 64
 __device__ __forceinline__ uint32_t digits_word(float x, float f) { return __float_as_uint(fmaf(x, f, 12615808.0f)); }
@@ -314,71 +303,133 @@ __device__ __forceinline__ void build_i8(Tables& T, const void* x, bool xf32, in
   }
 }
 
-// 3-bit tables: tab0[row][16 halves] holds the pre-scaled activations of the codes of packed row
-// `row` that belong to the row's first group, tab1[group][16 halves] those of the row that
-// straddles into `group` from the group before; half 2q+hi = code q + 5*hi of the row.
-// A warp takes up to four groups at a time so that their loads are in flight together.
+// 3-bit matrices on the integer path.  A packed word holds ten codes at bits 0, 3, .., 27; three
+// masks turn it into u8 operands: kind 0 = codes 0, 3, 6, 8 (one per byte, shifted left by
+// 0, 1, 2, 0 inside their bytes), kind 1 = codes 1, 4, 7, 9 (shifts 3, 4, 5, 3), kind 2 = codes 2
+// and 5, which straddle byte boundaries and are brought into bytes 0, 1 by a shift of the word
+// (shifts 0, 1); the kind-2 operands of two rows share a register.  The table holds, per digit
+// plane, two words per packed row (kinds 0, 1) and one word per row pair (r, r + 4: kind 2 of
+// both), every code scaled with its own group's exponent; a row whose codes fall into two groups
+// is masked when it is used.  A run is 64 rows = 640 k = 5 groups, so the group a code belongs
+// to is a fixed function of the row's position in the run.
 __device__ __forceinline__ int b3_rows(int K) { return (K + 9) / 10; }
+__device__ __forceinline__ int b3_rows_padded(int K) { return ((b3_rows(K) + 63) >> 6) << 6; }
+__device__ __forceinline__ int b3_stride_a(int K) { return 2 * b3_rows_padded(K) + 8; }
+__device__ __forceinline__ int b3_stride_k2(int K) { return b3_rows_padded(K) / 2 + 4; }
+
+// four digit words -> the three plane words of their four codes (byte i = code i)
+__device__ __forceinline__ void planes_of4(const uint32_t (&e)[4], uint32_t (&pl)[3]) {
+  const uint32_t x01 = __byte_perm(e[0], e[1], 0x5410), x23 = __byte_perm(e[2], e[3], 0x5410);
+  pl[0] = __byte_perm(x01, x23, 0x6420) ^ 0x80808080u;
+  pl[1] = __byte_perm(x01, x23, 0x7531) ^ 0x80808080u;
+  const uint32_t t = __byte_perm(__byte_perm(e[0], e[1], 0x0062), __byte_perm(e[2], e[3], 0x0062), 0x5410) ^ 0x40404040u;
+  pl[2] = t | ((t & 0x40404040u) << 1);  // sign-extend the 7-bit top digit
+}
+
 __device__ __forceinline__ void build_b3(Tables& T, const void* x, bool xf32, int K, unsigned need, const int* flags,
                                          int* err, int spin, int warp, int lane) {
-  const int rows = b3_rows(K), ngroups = K / kGroup;
-  uint32_t* tab1w = T.tab + rows * 8;
-  const int words = rows * 8 + ngroups * 8;
-  for (int i = warp * 32 + lane; i < words; i += kConsThreads) T.tab[i] = 0u;
+  const int ngroups = K / kGroup;
+  const int nruns = b3_rows_padded(K) >> 6;  // < 32: bit q of `need` = run q
+  need &= nruns >= 32 ? 0xffffffffu : ((1u << nruns) - 1u);
+  const int nwant = __popc(need);
+  // pass 1: exponent and sum of every group of the wanted runs.  Eight lanes per group, four
+  // groups per warp and batch: their flags are polled together, their loads are in flight together.
+  {
+    const int sub = lane >> 3, l8 = lane & 7;
+#pragma unroll 1
+    for (int i0 = 4 * warp; i0 < 5 * nwant; i0 += 4 * kCons) {
+      const int i = i0 + sub;
+      int my_g = -1;
+      if (i < 5 * nwant) {
+        const int run = __fns(need, 0, i / 5 + 1);
+        const int gq = 5 * run + i % 5;
+        if (gq < ngroups) my_g = gq;
+      }
+      if (flags) {
+        if (my_g >= 0 && l8 == 0) poll_flag(flags + my_g, err, spin);
+        __syncwarp();
+      }
+      float mx = 0.f, sm = 0.f;
+      if (my_g >= 0) {
+        const size_t k = static_cast<size_t>(my_g) * kGroup + 16 * l8;
+        if (xf32) {
+          const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + k);
+          float4 t[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) t[u] = __ldcg(p + u);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            mx = fmaxf(fmaxf(mx, fmaxf(fabsf(t[u].x), fabsf(t[u].y))), fmaxf(fabsf(t[u].z), fabsf(t[u].w)));
+            sm += (t[u].x + t[u].y) + (t[u].z + t[u].w);
+          }
+        } else {
+          const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(x) + k);
+          uint4 t[2] = {p[0], p[1]};
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const __half2* h = reinterpret_cast<const __half2*>(&t[u]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = __half22float2(h[q]);
+              mx = fmaxf(mx, fmaxf(fabsf(f.x), fabsf(f.y)));
+              sm += f.x + f.y;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        sm += __shfl_xor_sync(0xffffffffu, sm, o);
+      }
+      if (my_g >= 0 && l8 == 0) {
+        T.xsum[my_g] = sm;
+        T.fin[my_g] = pow2i(-scale_exp_i8(mx));
+      }
+    }
+  }
   bar_consumers();
-  __half* tab0 = reinterpret_cast<__half*>(T.tab);
-  __half* tab1 = reinterpret_cast<__half*>(tab1w);
-  int taken = 0, gq = 0;
-  while (gq < ngroups) {
-    int mine[4] = {0, 0, 0, 0}, nmine = 0;
-    for (; gq < ngroups && nmine < 4; ++gq) {
-      if (gq / 5 < 32 && !((need >> (gq / 5)) & 1u)) continue;
-      if ((taken++ % kCons) != warp) continue;
-      mine[nmine++] = gq;
+  // pass 2: a lane per packed row, the 32-row halves of the wanted runs round robin over the warps
+  const int sa = b3_stride_a(K), sk = b3_stride_k2(K);
+  uint32_t* tab_k2 = T.tab + 3 * sa;
+#pragma unroll 1
+  for (int i = warp; i < 2 * nwant; i += kCons) {
+    const int row = 64 * __fns(need, 0, (i >> 1) + 1) + 32 * (i & 1) + lane;
+    const int k0 = 10 * row;
+    const int g_lo = k0 >> 7;
+    const int j_hi = 128 * (g_lo + 1) - k0;  // first code of the row that belongs to the next group
+    const float f_lo = g_lo < ngroups ? __uint_as_float(0x7f000000u - __float_as_uint(T.fin[g_lo])) : 0.f;
+    const float f_hi = (j_hi < 10 && g_lo + 1 < ngroups) ? __uint_as_float(0x7f000000u - __float_as_uint(T.fin[g_lo + 1])) : 0.f;
+    float v[10];
+#pragma unroll
+    for (int j = 0; j < 10; ++j) {
+      const int k = k0 + j;
+      v[j] = 0.f;
+      if (k < K) v[j] = xf32 ? __ldcg(static_cast<const float*>(x) + k) : __half2float(static_cast<const __half*>(x)[k]);
     }
-    float xv[4][4];
-    if (flags) {  // lanes 0..3 poll the flags of the four groups together
-      const int gm = lane == 0 ? mine[0] : (lane == 1 ? mine[1] : (lane == 2 ? mine[2] : mine[3]));
-      if (lane < nmine) poll_flag(flags + gm, err, spin);
-      __syncwarp();
+    uint32_t e[10];
+#pragma unroll
+    for (int j = 0; j < 10; ++j) {
+      // position of code j inside its byte: kind 0 = codes 0,3,6,8 at 0,1,2,0; kind 1 = 1,4,7,9 at 3,4,5,3; kind 2 = 2,5 at 0,1
+      constexpr int sh[10] = {0, 3, 0, 1, 4, 1, 2, 5, 0, 3};
+      e[j] = digits_word(v[j], (j < j_hi ? f_lo : f_hi) * (1.0f / static_cast<float>(1 << sh[j])));
     }
+    uint32_t pl[3];
+    {
+      const uint32_t k0e[4] = {e[0], e[3], e[6], e[8]}, k1e[4] = {e[1], e[4], e[7], e[9]};
+      uint32_t p1[3];
+      planes_of4(k0e, pl);
+      planes_of4(k1e, p1);
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (u < nmine) {
+      for (int p = 0; p < 3; ++p) *reinterpret_cast<uint2*>(T.tab + p * sa + 2 * row) = make_uint2(pl[p], p1[p]);
+    }
+    const uint32_t e2p = __shfl_down_sync(0xffffffffu, e[2], 4), e5p = __shfl_down_sync(0xffffffffu, e[5], 4);
+    if ((lane & 4) == 0) {
+      const uint32_t k2e[4] = {e[2], e[5], e2p, e5p};
+      planes_of4(k2e, pl);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const size_t k = static_cast<size_t>(mine[u]) * kGroup + i * 32 + lane;
-          xv[u][i] = xf32 ? __ldcg(static_cast<const float*>(x) + k) : __half2float(static_cast<const __half*>(x)[k]);
-        }
-      }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (u < nmine) {
-        const int gg = mine[u];
-        float mx = 0.f, sm = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { mx = fmaxf(mx, fabsf(xv[u][i])); sm += xv[u][i]; }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-          sm += __shfl_xor_sync(0xffffffffu, sm, o);
-        }
-        const int c = scale_exp_b3(mx);
-        if (lane == 0) {
-          T.xsum[gg] = sm;
-          T.fin[gg] = pow2i(24 - c);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int e = gg * kGroup + i * 32 + lane;
-          const int row = e / 10, j = e - row * 10;
-          const int hi = j >= 5 ? 1 : 0, q = j - 5 * hi;
-          const int pos = 3 * (q < 3 ? q : q - 3);
-          const __half v = __float2half_rn(xv[u][i] * pow2i(c - pos));
-          if (gg == ((row * 10) >> 7)) tab0[row * 16 + 2 * q + hi] = v;
-          else tab1[gg * 16 + 2 * q + hi] = v;
-        }
-      }
+      for (int p = 0; p < 3; ++p) tab_k2[p * sk + 4 * (row >> 3) + (row & 3)] = pl[p];
+    }
   }
 }
 
@@ -695,15 +746,18 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
 }
 
 // ---- the load side of a consumer warp: walks the warp's tasks ahead of the compute side ------
-// A flush run (two groups; five for 3-bit) is a sequence of ring tasks: nt weight tasks of 4
-// packed rows x 128 columns, then nm "meta" tasks, task k carrying the scales | offsets
-// (256 + 256 bytes per group) of the run's groups 4k .. 4k+3.  The run is folded when its last
-// meta task arrives, reading the scales straight from the ring.
+// A flush run of a 1/2/4-bit matrix (two groups) is a sequence of ring tasks: nt weight tasks of 4
+// packed rows x 128 columns, then a "meta" task carrying the scales | offsets (256 + 256 bytes per
+// group) of the run's groups; the run is folded when the meta task arrives, reading the scales
+// straight from the ring.  A 3-bit run (64 packed rows, five groups) is a sequence of quads: four
+// weight tasks (16 rows) and a meta task with the group that ends inside the quad (the last quad
+// of a run: the two groups that end there), so that a group is folded as soon as it is complete.
 struct Loader {
   const uint32_t* w;    // lane's 16 bytes in row 0 of the next weight task
   const uint32_t* safe; // a valid address of the part's matrix for the zero-filled copies
   const __half* m;      // lane's 16 bytes of scales (lanes 0..15) / offsets (16..31) of group 0 of the run
-  int i, nt, ntot;      // next task of the run; weight tasks; weight + meta tasks
+  int i, nt, ntot;      // next task of the run; weight tasks (3-bit: quads); weight + meta tasks
+  int b3;               // 3-bit run layout
   int N;                // row pitch of the part's matrix (words, = halves of the scale rows)
   int rows_left;        // 3-bit: valid packed rows from the next weight task on (other widths: large)
   int ng;               // groups of the run
@@ -716,13 +770,9 @@ struct Loader {
 __device__ __forceinline__ int run_groups(int B, int run, int ngroups) {
   return B == 3 ? min(5, ngroups - 5 * run) : min(2, ngroups - 2 * run);
 }
-__device__ __forceinline__ int run_weight_tasks(int B, int run, int ngroups, int kw) {
-  if (B == 3) {
-    const int rows = min(64, kw - 64 * run);
-    return 2 * ((rows + 7) >> 3);
-  }
-  return min(2, ngroups - 2 * run) * B;
-}
+__device__ __forceinline__ int run_weight_tasks(int B, int run, int ngroups) { return min(2, ngroups - 2 * run) * B; }
+// quads (16 packed rows) of a 3-bit run
+__device__ __forceinline__ int b3_run_quads(int run, int kw) { return (min(64, kw - 64 * run) + 15) >> 4; }
 // first run of run lane kq in a part
 __device__ __forceinline__ int first_run(const PartDesc& d, int kq) { return d.run_lo + (kq + kLanes - d.roff) % kLanes; }
 
@@ -749,8 +799,14 @@ __device__ __forceinline__ void loader_next_run(Loader* Lp, const Smem* Sp, int 
   const int B = d.B;
   L.N = d.N;
   L.ng = run_groups(B, L.run, d.ngroups);
-  L.nt = run_weight_tasks(B, L.run, d.ngroups, d.kw);
-  L.ntot = L.nt + ((L.ng + 3) >> 2);
+  L.b3 = B == 3;
+  if (B == 3) {
+    L.nt = b3_run_quads(L.run, d.kw);
+    L.ntot = 5 * L.nt;
+  } else {
+    L.nt = run_weight_tasks(B, L.run, d.ngroups);
+    L.ntot = L.nt + 1;
+  }
   L.i = 0;
   const int row0 = (B == 3 ? 64 : 8 * B) * L.run;
   L.rows_left = B == 3 ? d.kw - row0 : (1 << 30);
@@ -764,7 +820,9 @@ __device__ __forceinline__ void loader_next_run(Loader* Lp, const Smem* Sp, int 
 __device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, int lane) {
   if (L.i < L.ntot) {
     const uint32_t dst = L.ring + L.slot * kSlotBytes;
-    if (L.i < L.nt) {
+    const int quad = L.i / 5, qpos = L.i - 5 * quad;  // 3-bit: position in the quad sequence
+    const bool meta = L.b3 ? qpos == 4 : L.i >= L.nt;
+    if (!meta) {
       // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
       const uint32_t* src = L.rows_left > 0 ? L.w : L.safe;
 #pragma unroll
@@ -775,12 +833,14 @@ __device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, in
       L.w += 4 * static_cast<size_t>(L.N);
       L.rows_left -= 4;
     } else {
-      // group h of the four: lanes 0..15 copy its 256 bytes of scales, lanes 16..31 its offsets
-      const int g0 = 4 * (L.i - L.nt);
+      // lanes 0..15 copy the 256 bytes of scales of a group, lanes 16..31 its offsets; 1/2/4-bit: the
+      // run's (up to two) groups; 3-bit: the group that ends in this quad, and the next one after the last quad
+      const int g0 = L.b3 ? quad : 0;
+      const int cnt = L.b3 ? (quad == L.nt - 1 ? 2 : 1) : 2;
       const __half* src = L.m + static_cast<size_t>(g0) * L.N;
 #pragma unroll
-      for (int h = 0; h < 4; ++h)
-        if (g0 + h < L.ng) {
+      for (int h = 0; h < 2; ++h)
+        if (h < cnt && g0 + h < L.ng) {
           cp_async16s(dst + 512 * h + 16 * lane, src, 16);
           src += L.N;
         }
@@ -871,91 +931,57 @@ __device__ __forceinline__ void fold_i8(RunState* Rp, const Tables* Tp, const un
       for (int e = 0; e < 4; ++e) R.acc[j][s][e] = 0;
 }
 
-// 3-bit: merge the two 15-bit halves of a word into fp16x2 lanes, then mask out code pairs.
-__device__ __forceinline__ uint32_t b3_merge(uint32_t w) { return (w & 0x00007fffu) | ((w << 1) & 0x7fff0000u); }
-__device__ __forceinline__ uint32_t b3_operand(uint32_t t, int q) {
-  return q < 3 ? (t & (0x00070007u << (3 * q))) : ((t >> 9) & (0x00070007u << (3 * (q - 3))));
-}
-
-// Weight tasks come in pairs (8 packed rows): the odd task of a pair does the work, lane c takes
-// rows 2c and 2c+1 of the pair, i.e. rows of the previous ring slot for c < 2.
-__device__ __forceinline__ void task_b3(RunState& R, const Tables& T, const uint32_t* zero_row, const unsigned char* prevp,
-                                        const unsigned char* slotp, int run, int i, int K, int kw, int ngroups, int lane) {
-  const int g = lane >> 2, c = lane & 3;
-  const int rows3 = b3_rows(K);
-  uint32_t bf[10];
-  const unsigned char* wp[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int lr = 2 * c + r;  // row inside the pair of tasks
-    const int row = 64 * run + 8 * (i >> 1) + lr;
-    wp[r] = (lr < 4 ? prevp : slotp) + ring_off(lr & 3, g);
-    const int d0 = (row * 10) >> 7, d1 = (row * 10 + 9) >> 7;
-    const int dl = d0 - 5 * run;
-    const uint32_t* bp = zero_row;
-    if (row < kw) {
-      if (g == dl) bp = T.tab + row * 8;
-      else if (g == dl + 1 && d1 != d0 && d1 < ngroups) bp = T.tab + rows3 * 8 + d1 * 8;
-    }
-    const uint4 t4 = *reinterpret_cast<const uint4*>(bp);
-    bf[5 * r + 0] = t4.x; bf[5 * r + 1] = t4.y; bf[5 * r + 2] = t4.z; bf[5 * r + 3] = t4.w;
-    bf[5 * r + 4] = bp[4];
-  }
+// A pair of 3-bit weight tasks (8 packed rows): lane c takes row c of the even task (`ep`) and
+// row c of the odd one (`op`), i.e. rows i and i + 4 of the pair.  Per column pair three MMAs:
+// kinds 0 | 1 of each row, then the kind-2 operands of both rows in one register.  `b` = the
+// lane's B words (already masked to the group its MMA column serves): kinds 0, 1 of the even
+// row, of the odd row, kind 2 of the pair.
+__device__ __forceinline__ void pair_b3(RunState& R, const unsigned char* ep, const unsigned char* op, const uint32_t (&b)[5]) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    uint32_t mw[2][4];
+    const uint4 we = *reinterpret_cast<const uint4*>(ep + 128 * j);
+    const uint4 wo = *reinterpret_cast<const uint4*>(op + 128 * j);
+    const uint32_t ev[4] = {we.x, we.y, we.z, we.w}, ov[4] = {wo.x, wo.y, wo.z, wo.w};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const uint4 w = *reinterpret_cast<const uint4*>(wp[r] + 128 * j);
-      mw[r][0] = b3_merge(w.x); mw[r][1] = b3_merge(w.y); mw[r][2] = b3_merge(w.z); mw[r][3] = b3_merge(w.w);
+    for (int s = 0; s < 2; ++s) {
+      const uint32_t e0 = ev[2 * s], e1 = ev[2 * s + 1], o0 = ov[2 * s], o1 = ov[2 * s + 1];
+      mma_u8s8(R.acc[j][s], e0 & 0x071c0e07u, e1 & 0x071c0e07u, e0 & 0x38e07038u, e1 & 0x38e07038u, b[0], b[1]);
+      mma_u8s8(R.acc[j][s], o0 & 0x071c0e07u, o1 & 0x071c0e07u, o0 & 0x38e07038u, o1 & 0x38e07038u, b[2], b[3]);
+      const uint32_t x0 = ((e0 >> 6) & 0x00000e07u) | ((o0 << 10) & 0x0e070000u);
+      const uint32_t x1 = ((e1 >> 6) & 0x00000e07u) | ((o1 << 10) & 0x0e070000u);
+      mma_u8s8(R.acc[j][s], x0, x1, 0u, 0u, b[4], 0u);
     }
-#pragma unroll
-    for (int mm = 0; mm < 5; ++mm)
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const int s0 = 2 * mm, s1 = 2 * mm + 1;
-        const uint32_t a0 = s0 < 5 ? b3_operand(mw[0][2 * s], s0) : b3_operand(mw[1][2 * s], s0 - 5);
-        const uint32_t a1 = s0 < 5 ? b3_operand(mw[0][2 * s + 1], s0) : b3_operand(mw[1][2 * s + 1], s0 - 5);
-        const uint32_t a2 = s1 < 5 ? b3_operand(mw[0][2 * s], s1) : b3_operand(mw[1][2 * s], s1 - 5);
-        const uint32_t a3 = s1 < 5 ? b3_operand(mw[0][2 * s + 1], s1) : b3_operand(mw[1][2 * s + 1], s1 - 5);
-        mma_f16(R.acc[j][s], a0, a1, a2, a3, bf[s0], bf[s1]);
-      }
   }
 }
 
-// Fold a 3-bit run: C column d of a tile holds run-local group d; groups 0..3 sit in the first
-// meta task (`m0`), group 4 in the second (`m1`).
-__device__ __forceinline__ void fold_b3(RunState* Rp, const Tables* Tp, const unsigned char* m0, const unsigned char* m1,
-                                     int run, int ng, int lane) {
+// Fold the MMA columns of one or both groups of a 3-bit quad into the running sums.  C columns
+// 2c, 2c+1 of lane c hold digit planes 2(c&1), 2(c&1)+1 of the group served by half c >> 1 of the
+// MMA columns; `grp` = that group, `slot` = its place in the meta task `mp`, `on` = fold it now.
+__device__ __forceinline__ void fold_b3(RunState* Rp, const Tables* Tp, const unsigned char* mp, int grp, int slot, bool on,
+                                        int lane) {
   RunState& R = *Rp;
   const Tables& T = *Tp;
   const int g = lane >> 2, c = lane & 3;
+  if (on) {
+    const float f0 = T.fin[grp] * ((c & 1) ? 65536.0f : 1.0f), f1 = f0 * 256.0f;
+    const float xs = (c & 1) ? 0.f : T.xsum[grp];
+    const unsigned char* gp = mp + 512 * slot + 8 * g;
 #pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    const int d = 2 * c + p;
-    if (d < ng) {
-      const int grp = 5 * run + d;
-      const float fin = T.fin[grp], xs = T.xsum[grp];
-      const unsigned char* gp = (d < 4 ? m0 : m1) + 512 * (d & 3) + 8 * g;
+    for (int j = 0; j < 4; ++j) {
+      float sc[4], zr[4];
+      unpack4(*reinterpret_cast<const uint2*>(gp + 64 * j), sc);
+      unpack4(*reinterpret_cast<const uint2*>(gp + 256 + 64 * j), zr);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float sc[4], zr[4];
-        unpack4(*reinterpret_cast<const uint2*>(gp + 64 * j), sc);
-        unpack4(*reinterpret_cast<const uint2*>(gp + 256 + 64 * j), zr);
+      for (int s = 0; s < 2; ++s) {
+        const float ta = fmaf(f1, __int2float_rn(R.acc[j][s][1]), f0 * __int2float_rn(R.acc[j][s][0]));
+        const float tb = fmaf(f1, __int2float_rn(R.acc[j][s][3]), f0 * __int2float_rn(R.acc[j][s][2]));
+        R.vs[j][s][0] += fmaf(sc[2 * s], ta, zr[2 * s] * xs);
+        R.vs[j][s][1] += fmaf(sc[2 * s + 1], tb, zr[2 * s + 1] * xs);
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          R.vs[j][s][0] += fmaf(sc[2 * s] * fin, __int_as_float(R.acc[j][s][p]), zr[2 * s] * xs);
-          R.vs[j][s][1] += fmaf(sc[2 * s + 1] * fin, __int_as_float(R.acc[j][s][2 + p]), zr[2 * s + 1] * xs);
-        }
+        for (int e = 0; e < 4; ++e) R.acc[j][s][e] = 0;
       }
     }
   }
-#pragma unroll
-  for (int j = 0; j < 4; ++j)
-#pragma unroll
-    for (int s = 0; s < 2; ++s)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) R.acc[j][s][e] = 0;
 }
 
 // The compute side's position in its ring.
@@ -1003,42 +1029,79 @@ __device__ __forceinline__ void part_i8(RunState& R, Loader& L, Cursor& C, const
   }
 }
 
-__device__ __forceinline__ void part_b3(RunState& R, Loader& L, Cursor& C, const Smem& S, const PartDesc& d,
-                                        const uint32_t* zero_row, int kq, int lane) {
+// All runs of run lane kq in a 3-bit part.
+__device__ __forceinline__ void part_b3(RunState& R, Loader& L, Cursor& C, const Smem& S, const PartDesc& d, int kq, int lane) {
   const int K = d.ngroups * kGroup;
+  const int g = lane >> 2, c = lane & 3;
+  const int woff = ring_off(c, g);
+  // this lane's MMA column: digit plane (g & 3) for the even (g < 4) or odd group of the quad; column 3 / 7 stays empty
+  const bool feeds = (g & 3) < 3;
+  const uint32_t* tab_a = S.T.tab + (g & 3) * b3_stride_a(K);
+  const uint32_t* tab_k2 = S.T.tab + 3 * b3_stride_a(K) + (g & 3) * b3_stride_k2(K);
   const int run_hi = d.run_hi;
 #pragma unroll 1
   for (int run = first_run(d, kq); run < run_hi; run += kLanes) {
     const int ng = min(5, d.ngroups - 5 * run);
-    const int nt = run_weight_tasks(3, run, d.ngroups, d.kw);
-    const unsigned char* prev = nullptr;
+    const int nquads = b3_run_quads(run, d.kw);
 #pragma unroll 1
-    for (int i = 0; i < nt; ++i) {
-      const unsigned char* slotp = cursor_take(C);
-      if (i & 1) task_b3(R, S.T, zero_row, prev, slotp, run, i, K, d.kw, d.ngroups, lane);
-      prev = slotp;
-      __syncwarp();  // every lane is done with `prev` of the last pair before its slot is refilled
+    for (int quad = 0; quad < nquads; ++quad) {
+      // groups of the quad: ga ends at local row 12 - 3 * quad, whose codes from 8 - 2 * quad on belong to ga + 1
+      const int ga = 5 * run + quad;
+      const bool is_a = ((ga ^ (g >> 2)) & 1) == 0;  // does this lane's half of the MMA columns serve ga
+      const int brow = 12 - 3 * quad;
+      // bytes of the boundary row that belong to ga + 1, per kind (codes 0,3,6,8 | 1,4,7,9 | 2,5)
+      const uint32_t mb0 = quad == 0 ? 0xff000000u : (quad == 3 ? 0xffffff00u : 0xffff0000u);
+      const uint32_t mb1 = quad == 0 ? 0xff000000u : (quad == 1 ? 0xffff0000u : 0xffffff00u);
+      const uint32_t mb2 = quad < 2 ? 0u : (quad == 2 ? 0xff00u : 0xffffu);
+      const unsigned char* prev = nullptr;
+#pragma unroll 1
+      for (int t = 0; t < 4; ++t) {
+        const unsigned char* slotp = cursor_take(C);
+        if (t & 1) {
+          const int row = 64 * run + 16 * quad + 4 * (t - 1) + c;  // even task's row; the odd one's is row + 4
+          uint32_t b[5] = {0u, 0u, 0u, 0u, 0u};
+          if (feeds) {
+            const uint2 be = *reinterpret_cast<const uint2*>(tab_a + 2 * row);
+            const uint2 bo = *reinterpret_cast<const uint2*>(tab_a + 2 * (row + 4));
+            const uint32_t bk = tab_k2[4 * (row >> 3) + (row & 3)];
+            const int ie = 4 * (t - 1) + c, io = ie + 4;  // local rows in the quad
+            // mask of the bytes that belong to this lane's group, for the even and the odd row
+            const uint32_t full = is_a ? 0xffffffffu : 0u;
+            const uint32_t me0 = ie < brow ? full : (ie > brow ? ~full : (is_a ? ~mb0 : mb0));
+            const uint32_t me1 = ie < brow ? full : (ie > brow ? ~full : (is_a ? ~mb1 : mb1));
+            const uint32_t me2 = ie < brow ? full : (ie > brow ? ~full : (is_a ? ~mb2 : mb2));
+            const uint32_t mo0 = io < brow ? full : (io > brow ? ~full : (is_a ? ~mb0 : mb0));
+            const uint32_t mo1 = io < brow ? full : (io > brow ? ~full : (is_a ? ~mb1 : mb1));
+            const uint32_t mo2 = io < brow ? full : (io > brow ? ~full : (is_a ? ~mb2 : mb2));
+            b[0] = be.x & me0; b[1] = be.y & me1;
+            b[2] = bo.x & mo0; b[3] = bo.y & mo1;
+            b[4] = bk & ((me2 & 0xffffu) | (mo2 << 16));
+          }
+          pair_b3(R, prev + woff, slotp + woff, b);
+          __syncwarp();  // every lane is done with `prev` before its slot is refilled
+        }
+        prev = slotp;
+        loader_step(L, S, kq, lane);
+      }
+      const unsigned char* mp = cursor_take(C);
+      // the group that ends in this quad; after the last quad of the run also the one after it
+      // (the lane's accumulator columns 2c, 2c+1 lie in half c >> 1 of the MMA columns)
+      const bool last = quad == nquads - 1;
+      const bool acc_a = ((ga ^ (c >> 1)) & 1) == 0;
+      const int grp = acc_a ? ga : ga + 1;
+      const bool on = (acc_a || last) && grp - 5 * run < ng;
+      fold_b3(&R, &S.T, mp, grp, acc_a ? 0 : 1, on, lane);
       loader_step(L, S, kq, lane);
     }
-    const unsigned char* m0 = cursor_take(C);
-    const unsigned char* m1 = m0;
-    if (ng > 4) {
-      __syncwarp();
-      loader_step(L, S, kq, lane);
-      m1 = cursor_take(C);
-    }
-    fold_b3(&R, &S.T, m0, m1, run, ng, lane);
-    __syncwarp();
-    loader_step(L, S, kq, lane);
   }
 }
 
-__device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zero_row, int* err) {
+__device__ void consumer_role(Smem& S, const FusedParams& P, int* err) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kq = warp;
   const int g = lane >> 2, c = lane & 3;
   Loader L;
-  L.p = -1; L.run = 0; L.run_hi = 0; L.i = 0; L.nt = 0; L.ntot = 0; L.N = 0; L.rows_left = 0; L.ng = 0;
+  L.p = -1; L.run = 0; L.run_hi = 0; L.i = 0; L.nt = 0; L.ntot = 0; L.N = 0; L.rows_left = 0; L.ng = 0; L.b3 = 0;
   L.w = nullptr; L.m = nullptr; L.safe = nullptr;
   L.slot = 0;
   L.ring = smem_u32(S.ring[warp][0]);
@@ -1091,7 +1154,7 @@ __device__ void consumer_role(Smem& S, const FusedParams& P, const uint32_t* zer
     if (B == 1) part_i8<1>(R, L, C, S, d, kq, lane);
     else if (B == 2) part_i8<2>(R, L, C, S, d, kq, lane);
     else if (B == 4) part_i8<4>(R, L, C, S, d, kq, lane);
-    else part_b3(R, L, C, S, d, zero_row, kq, lane);
+    else part_b3(R, L, C, S, d, kq, lane);
     // end of the part: fold the MMA columns of the four lanes of a row, hand the columns to the finisher
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -1350,7 +1413,6 @@ __device__ void finisher_role(Smem& S, const FusedParams& P, int* err) {
 __global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_constant__ FusedParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Smem& S = *reinterpret_cast<Smem*>(smem_raw);
-  __shared__ __align__(16) uint32_t zero_row[16];
   const int warp = threadIdx.x >> 5;
   int* err = P.counters + kErrSlot;
   if (threadIdx.x == 0) {
@@ -1360,7 +1422,6 @@ __global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_co
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (threadIdx.x < 16) zero_row[threadIdx.x] = 0u;
   // Ahead of the dependency wait: what does not depend on earlier kernels.  The per-expert bit
   // widths and offsets go to shared memory, the router matrix is pulled into L2.
   if (P.E <= kMetaE) {
@@ -1410,7 +1471,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_decode_kernel(const __grid_co
   if (warp == 0) make_plan(S, P);
   __syncthreads();
   if (S.overflow && threadIdx.x == 0) atomicExch(err, 14);
-  if (warp < kCons) consumer_role(S, P, zero_row, err);
+  if (warp < kCons) consumer_role(S, P, err);
   else finisher_role(S, P, err);
   __syncthreads();
   if (threadIdx.x == 0) {
