@@ -137,7 +137,7 @@ struct Smem {
   alignas(8) unsigned long long redfull[kRedSlots], redempty[kRedSlots];
   SlotInfo slot[kMaxS];
   PartDesc parts[kMaxParts];
-  int n_parts, n_parts0, expected1, pairs_total, overflow;
+  int n_parts, expected1, pairs_total, overflow;
   int spin;  // polls a bounded wait may take
   int sel_e[kMaxS];
   __half sel_w[kMaxS];
@@ -731,7 +731,6 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
       }
     }
     pbase += np_total;
-    if (ph == 0 && lane == 0) S.n_parts0 = pbase;
   }
   __syncwarp();
   if (lane == 0) {
@@ -817,33 +816,43 @@ __device__ __forceinline__ void loader_next_run(Loader* Lp, const Smem* Sp, int 
 
 // Issue the copies of the loader's next task (one commit group per call, empty when the warp
 // has run out of tasks) and step to the task after it.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// (The loader runs ahead of the compute side: the form of ITS run decides, not the part being computed.)
 __device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, int lane) {
   if (L.i < L.ntot) {
     const uint32_t dst = L.ring + L.slot * kSlotBytes;
-    const int quad = L.i / 5, qpos = L.i - 5 * quad;  // 3-bit: position in the quad sequence
-    const bool meta = L.b3 ? qpos == 4 : L.i >= L.nt;
-    if (!meta) {
-      // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
-      const uint32_t* src = L.rows_left > 0 ? L.w : L.safe;
+    if (!L.b3) {
+      if (L.i < L.nt) {
+        const char* src = reinterpret_cast<const char*>(L.w);
+        const size_t pitch = static_cast<size_t>(L.N) * 4;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        cp_async16s(dst + L.roff[r], src, r < L.rows_left ? 16 : 0);
-        if (r < 3 && r + 1 < L.rows_left) src += L.N;
+        for (int r = 0; r < 4; ++r) cp_async16(dst + L.roff[r], src + r * pitch);
+        L.w += 4 * static_cast<size_t>(L.N);
+      } else {
+        // lanes 0..15 copy the 256 bytes of scales of a group, lanes 16..31 its offsets
+        cp_async16(dst + 16 * lane, L.m);
+        if (L.ng > 1) cp_async16(dst + 512 + 16 * lane, L.m + L.N);
       }
-      L.w += 4 * static_cast<size_t>(L.N);
-      L.rows_left -= 4;
     } else {
-      // lanes 0..15 copy the 256 bytes of scales of a group, lanes 16..31 its offsets; 1/2/4-bit: the
-      // run's (up to two) groups; 3-bit: the group that ends in this quad, and the next one after the last quad
-      const int g0 = L.b3 ? quad : 0;
-      const int cnt = L.b3 ? (quad == L.nt - 1 ? 2 : 1) : 2;
-      const __half* src = L.m + static_cast<size_t>(g0) * L.N;
+      const int quad = L.i / 5, qpos = L.i - 5 * quad;  // position in the quad sequence
+      if (qpos < 4) {
+        // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
+        const uint32_t* src = L.rows_left > 0 ? L.w : L.safe;
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-        if (h < cnt && g0 + h < L.ng) {
-          cp_async16s(dst + 512 * h + 16 * lane, src, 16);
-          src += L.N;
+        for (int r = 0; r < 4; ++r) {
+          cp_async16s(dst + L.roff[r], src, r < L.rows_left ? 16 : 0);
+          if (r < 3 && r + 1 < L.rows_left) src += L.N;
         }
+        L.rows_left -= 4;
+        L.w += 4 * static_cast<size_t>(L.N);
+      } else {
+        // the group that ends in this quad, and the next one after the last quad of the run
+        const __half* src = L.m + static_cast<size_t>(quad) * L.N;
+        if (quad < L.ng) cp_async16(dst + 16 * lane, src);
+        if (quad == L.nt - 1 && quad + 1 < L.ng) cp_async16(dst + 512 + 16 * lane, src + L.N);
+      }
     }
     if (++L.i == L.ntot) loader_next_run(&L, &S, kq, lane, 0);
   }
@@ -864,26 +873,24 @@ __device__ __forceinline__ void unpack4(const uint2& r, float (&f)[4]) {
 }
 
 // Weight task of a 1/2/4-bit run: `wp` = lane's row c, quad g in the ring slot, `bp` = lane's B
-// operand words of that row (nullptr: this lane's MMA column is not fed by the task's group).
+// operand words of that row, `on` = the lane's MMA column is fed by the task's group (else zeros).
 template <int B>
-__device__ __forceinline__ void task_i8(RunState& R, const unsigned char* wp, const uint32_t* bp) {
+__device__ __forceinline__ void task_i8(RunState& R, const unsigned char* wp, const uint32_t* bp, bool on) {
   using F = I8<B>;
   constexpr int CPB = F::kCpb;
   uint32_t bf[CPB];
+  if (CPB >= 4) {
 #pragma unroll
-  for (int q = 0; q < CPB; ++q) bf[q] = 0u;
-  if (bp) {
-    if (CPB >= 4) {
-#pragma unroll
-      for (int q4 = 0; q4 < CPB / 4; ++q4) {
-        const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
-        bf[4 * q4] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
-      }
-    } else {
-      const uint2 t = *reinterpret_cast<const uint2*>(bp);
-      bf[0] = t.x; bf[1] = t.y;
+    for (int q4 = 0; q4 < CPB / 4; ++q4) {
+      const uint4 t = *reinterpret_cast<const uint4*>(bp + 4 * q4);
+      bf[4 * q4] = t.x; bf[4 * q4 + 1] = t.y; bf[4 * q4 + 2] = t.z; bf[4 * q4 + 3] = t.w;
     }
+  } else {
+    const uint2 t = *reinterpret_cast<const uint2*>(bp);
+    bf[0] = t.x; bf[1] = t.y;
   }
+#pragma unroll
+  for (int q = 0; q < CPB; ++q) bf[q] = on ? bf[q] : 0u;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint4 w = *reinterpret_cast<const uint4*>(wp + 128 * j);
@@ -1005,7 +1012,7 @@ __device__ __forceinline__ void part_i8(RunState& R, Loader& L, Cursor& C, const
   const int K = d.ngroups * kGroup;
   const int woff = ring_off(c, g);
   // this lane's MMA column: digit plane (g & 3) of the first (g < 4) or second group of a run; column 3 / 7 stays empty
-  const uint32_t* plane = S.T.tab + (g & 3) * F::plane_stride(K) + c * F::kCpb;
+  const uint32_t* plane = S.T.tab + min(g & 3, 2) * F::plane_stride(K) + c * F::kCpb;  // columns 3 / 7: switched off below
   const bool feeds = (g & 3) < 3;
   const int run_hi = d.run_hi;
 #pragma unroll 1
@@ -1018,7 +1025,7 @@ __device__ __forceinline__ void part_i8(RunState& R, Loader& L, Cursor& C, const
 #pragma unroll 1
       for (int ii = 0; ii < B; ++ii) {
         const unsigned char* slotp = cursor_take(C);
-        task_i8<B>(R, slotp + woff, on ? bp : nullptr);
+        task_i8<B>(R, slotp + woff, bp, on);
         bp += 4 * F::kCpb;
         loader_step(L, S, kq, lane);
       }
