@@ -169,7 +169,7 @@ __device__ __forceinline__ int quantum_groups(int bits) { return bits == 3 ? 5 :
 // (relative time of a quantum measured in place: the low bit widths are bound by the MMA and
 // logic issue rate, not by their bytes)
 __device__ __forceinline__ unsigned quantum_cost(int bits) {
-  return bits == 1 ? 32u : (bits == 2 ? 36u : (bits == 3 ? 74u : 49u));
+  return bits == 1 ? 32u : (bits == 2 ? 39u : (bits == 3 ? 86u : 54u));
 }
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
