@@ -46,8 +46,8 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=8)
     p.add_argument("--no-prefill", action="store_true", help="leave the config-3 sub-record out")
-    p.add_argument("--mode", default="bench", choices=["bench", "layer_only", "prefill_only", "generate"],
-                   help="layer_only / prefill_only: a short eager loop of one op for profilers; generate: the full "
+    p.add_argument("--mode", default="bench", choices=["bench", "layer_only", "prefill_only", "cfg2_only", "generate"],
+                   help="layer_only / prefill_only / cfg2_only: a short eager loop of one op for profilers; generate: the full "
                         "32-layer decoder (config 4), 512-token prompt, 256 greedy tokens; each prints its own JSON")
     p.add_argument("--batch", type=int, default=1, help="generate mode: sequences decoded together")
     p.add_argument("--gen-layers", type=int, default=32)
@@ -233,6 +233,17 @@ def profile_loop(args, dev):
         x, w, sel = x.to(dev), w.to(dev), sel.to(dev)
         once = lambda i: blk._prefill(x, 1, True, routing=(w, sel))
         extra = {"tokens": T, "bits": blk._nbits_host}
+    elif args.mode == "cfg2_only":
+        B = args.batch
+        blk = synth.deepseek_block(seed=0, device=dev)
+        xs = [torch.randn(B, 1, 2048, device=dev, generator=torch.Generator(device=dev).manual_seed(10 * B + i)).half()
+              for i in range(8)]
+        once = lambda i: blk(xs[0])  # one activation: the bytes below are those of every call
+        _, _, idx = blk._decode(xs[0].view(B, 2048), 2)
+        distinct = sorted(set(idx.view(-1).tolist()))
+        extra = {"batch": B, "distinct_experts": len(distinct),
+                 "algorithmic_bytes": sum(3 * 2048 * 1408 * (blk._nbits_host[e] + 0.25) / 8 for e in distinct)
+                 + 3 * 2048 * 2816 * 4.25 / 8 + 2 * 64 * 2048}
     else:
         L = args.layers
         blocks = [synth.mixtral_block(seed=LAYER_SEED0 + i, device=dev) for i in range(L)]

@@ -753,18 +753,21 @@ __device__ void make_plan(Smem& S, const FusedParams& P) {
 // of a run: the two groups that end there), so that a group is folded as soon as it is complete.
 struct Loader {
   const uint32_t* w;    // lane's 16 bytes in row 0 of the next weight task
-  const uint32_t* safe; // a valid address of the part's matrix for the zero-filled copies
-  const __half* m;      // lane's 16 bytes of scales (lanes 0..15) / offsets (16..31) of group 0 of the run
   int i, nt, ntot;      // next task of the run; weight tasks (3-bit: quads); weight + meta tasks
   int b3;               // 3-bit run layout
   int N;                // row pitch of the part's matrix (words, = halves of the scale rows)
-  int rows_left;        // 3-bit: valid packed rows from the next weight task on (other widths: large)
-  int ng;               // groups of the run
-  int run, run_hi, p;   // current run, end of the part's runs, part
+  int rows_left;        // 3-bit: valid packed rows from the next weight task on (other widths: unused)
+  int run, p;           // current run, part
   int slot;             // ring slot of the next task
   uint32_t ring;        // shared address of the warp's ring
   uint32_t roff[4];     // lane's position inside a weight task, per row
 };
+// What a step needs once per run is read from the part in shared memory instead of being carried
+// in registers (the kernel sits at its register limit): the lane's scales (lanes 0..15) or offsets
+// (lanes 16..31) of group 0 of the run, and the groups of the run.
+__device__ __forceinline__ const __half* loader_meta(const Loader& L, const PartDesc& d, int lane) {
+  return ((lane & 16) ? d.zr : d.sc) + static_cast<size_t>((L.b3 ? 5 : 2) * L.run) * d.N + 8 * (lane & 15);
+}
 
 __device__ __forceinline__ int run_groups(int B, int run, int ngroups) {
   return B == 3 ? min(5, ngroups - 5 * run) : min(2, ngroups - 2 * run);
@@ -788,16 +791,13 @@ __device__ __forceinline__ void loader_next_run(Loader* Lp, const Smem* Sp, int 
   Loader& L = *Lp;
   const Smem& S = *Sp;
   if (!first) L.run += kLanes;
-  while (L.p < 0 || L.run >= L.run_hi) {
+  while (L.p < 0 || L.run >= S.parts[L.p].run_hi) {
     if (++L.p >= S.n_parts) { L.ntot = 0; L.i = 0; return; }
-    const PartDesc& d = S.parts[L.p];
-    L.run_hi = d.run_hi;
-    L.run = first_run(d, kq);
+    L.run = first_run(S.parts[L.p], kq);
   }
   const PartDesc& d = S.parts[L.p];
   const int B = d.B;
   L.N = d.N;
-  L.ng = run_groups(B, L.run, d.ngroups);
   L.b3 = B == 3;
   if (B == 3) {
     L.nt = b3_run_quads(L.run, d.kw);
@@ -810,8 +810,6 @@ __device__ __forceinline__ void loader_next_run(Loader* Lp, const Smem* Sp, int 
   const int row0 = (B == 3 ? 64 : 8 * B) * L.run;
   L.rows_left = B == 3 ? d.kw - row0 : (1 << 30);
   L.w = d.w + static_cast<size_t>(row0) * d.N + 4 * lane;
-  L.safe = d.w + 4 * lane;
-  L.m = ((lane & 16) ? d.zr : d.sc) + static_cast<size_t>((B == 3 ? 5 : 2) * L.run) * d.N + 8 * (lane & 15);
 }
 
 // Issue the copies of the loader's next task (one commit group per call, empty when the warp
@@ -832,14 +830,16 @@ __device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, in
         L.w += 4 * static_cast<size_t>(L.N);
       } else {
         // lanes 0..15 copy the 256 bytes of scales of a group, lanes 16..31 its offsets
-        cp_async16(dst + 16 * lane, L.m);
-        if (L.ng > 1) cp_async16(dst + 512 + 16 * lane, L.m + L.N);
+        const PartDesc& d = S.parts[L.p];
+        const __half* m = loader_meta(L, d, lane);
+        cp_async16(dst + 16 * lane, m);
+        if (d.ngroups - 2 * L.run > 1) cp_async16(dst + 512 + 16 * lane, m + L.N);
       }
     } else {
       const int quad = L.i / 5, qpos = L.i - 5 * quad;  // position in the quad sequence
       if (qpos < 4) {
         // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
-        const uint32_t* src = L.rows_left > 0 ? L.w : L.safe;
+        const uint32_t* src = L.rows_left > 0 ? L.w : S.parts[L.p].w + 4 * lane;
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           cp_async16s(dst + L.roff[r], src, r < L.rows_left ? 16 : 0);
@@ -849,9 +849,11 @@ __device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, in
         L.w += 4 * static_cast<size_t>(L.N);
       } else {
         // the group that ends in this quad, and the next one after the last quad of the run
-        const __half* src = L.m + static_cast<size_t>(quad) * L.N;
-        if (quad < L.ng) cp_async16(dst + 16 * lane, src);
-        if (quad == L.nt - 1 && quad + 1 < L.ng) cp_async16(dst + 512 + 16 * lane, src + L.N);
+        const PartDesc& d = S.parts[L.p];
+        const int ng = min(5, d.ngroups - 5 * L.run);
+        const __half* src = loader_meta(L, d, lane) + static_cast<size_t>(quad) * L.N;
+        if (quad < ng) cp_async16(dst + 16 * lane, src);
+        if (quad == L.nt - 1 && quad + 1 < ng) cp_async16(dst + 512 + 16 * lane, src + L.N);
       }
     }
     if (++L.i == L.ntot) loader_next_run(&L, &S, kq, lane, 0);
@@ -1108,8 +1110,8 @@ __device__ void consumer_role(Smem& S, const FusedParams& P, int* err) {
   const int kq = warp;
   const int g = lane >> 2, c = lane & 3;
   Loader L;
-  L.p = -1; L.run = 0; L.run_hi = 0; L.i = 0; L.nt = 0; L.ntot = 0; L.N = 0; L.rows_left = 0; L.ng = 0; L.b3 = 0;
-  L.w = nullptr; L.m = nullptr; L.safe = nullptr;
+  L.p = -1; L.run = 0; L.i = 0; L.nt = 0; L.ntot = 0; L.N = 0; L.rows_left = 0; L.b3 = 0;
+  L.w = nullptr;
   L.slot = 0;
   L.ring = smem_u32(S.ring[warp][0]);
 #pragma unroll
