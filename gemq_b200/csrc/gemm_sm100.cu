@@ -512,26 +512,48 @@ __global__ void to_half_kernel(const T* __restrict__ x, __half* __restrict__ y, 
 // rounded to the activation dtype (index_add_ in the loop of moe_block.py:191-195), then the
 // shared-expert output (moe_block.py:483).
 template <typename T>
-__global__ void prefill_combine_kernel(const int* __restrict__ inv, const long long* __restrict__ idx,
-                                       const __half* __restrict__ ys, const __half* __restrict__ shared,
-                                       T* __restrict__ out, int tokens, int A, int D) {
+__global__ void __launch_bounds__(128) prefill_combine_kernel(const int* __restrict__ inv, const long long* __restrict__ idx,
+                                                              const __half* __restrict__ ys, const __half* __restrict__ shared,
+                                                              T* __restrict__ out, int tokens, int A, int D) {
+  __shared__ int rows[kMaxSlots];
   const int t = blockIdx.x;
-  int order[kMaxSlots];
-  for (int a = 0; a < A; ++a) order[a] = a;
-  for (int a = 1; a < A; ++a)  // insertion sort of the slots by expert id
-    for (int b = a; b > 0 && idx[t * A + order[b]] < idx[t * A + order[b - 1]]; --b) {
-      const int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
-    }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f;
+  if (threadIdx.x == 0) {
+    int order[kMaxSlots];
+    for (int a = 0; a < A; ++a) order[a] = a;
+    for (int a = 1; a < A; ++a)  // insertion sort of the slots by expert id
+      for (int b = a; b > 0 && idx[t * A + order[b]] < idx[t * A + order[b - 1]]; --b) {
+        const int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
+      }
+    for (int a = 0; a < A; ++a) rows[a] = inv[t * A + order[a]];
+  }
+  __syncthreads();
+  // eight columns per thread and step: one 16-byte load per expert row
+  for (int i = threadIdx.x; i < D / 8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
     for (int a = 0; a < A; ++a) {
-      const int row = inv[t * A + order[a]];
+      const int row = rows[a];
       if (row < 0) continue;  // pair with an expert id out of range
-      const float c = ActT<T>::f(ActT<T>::r(__half2float(ys[static_cast<size_t>(row) * D + d])));
-      acc = ActT<T>::f(ActT<T>::r(acc + c));
+      const uint4 v = reinterpret_cast<const uint4*>(ys + static_cast<size_t>(row) * D)[i];
+      const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float c = ActT<T>::f(ActT<T>::r(__half2float(h[k])));
+        acc[k] = ActT<T>::f(ActT<T>::r(acc[k] + c));
+      }
     }
-    if (shared) acc = ActT<T>::f(ActT<T>::r(acc + ActT<T>::f(ActT<T>::r(__half2float(shared[static_cast<size_t>(t) * D + d])))));
-    out[static_cast<size_t>(t) * D + d] = ActT<T>::r(acc);
+    if (shared) {
+      const uint4 v = reinterpret_cast<const uint4*>(shared + static_cast<size_t>(t) * D)[i];
+      const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = ActT<T>::f(ActT<T>::r(acc[k] + ActT<T>::f(ActT<T>::r(__half2float(h[k])))));
+    }
+    uint4 o;
+    T* q = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) q[k] = ActT<T>::r(acc[k]);
+    reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * D)[i] = o;
   }
 }
 
@@ -756,11 +778,11 @@ extern "C" int gemq_moe_prefill(const gemq_moe_layer_t* L, const void* x, void* 
     if (int rc = launch_gemm(SD, false, false, cdiv(tokens, kGemmBM), st)) return rc;
   }
   if (bf)
-    prefill_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, st>>>(
+    prefill_combine_kernel<__nv_bfloat16><<<tokens, 128, 0, st>>>(
         S.plan.inv, reinterpret_cast<const long long*>(idx), static_cast<const __half*>(S.ys),
         SF ? static_cast<const __half*>(S.yss) : nullptr, static_cast<__nv_bfloat16*>(out), tokens, A, D);
   else
-    prefill_combine_kernel<__half><<<tokens, 256, 0, st>>>(
+    prefill_combine_kernel<__half><<<tokens, 128, 0, st>>>(
         S.plan.inv, reinterpret_cast<const long long*>(idx), static_cast<const __half*>(S.ys),
         SF ? static_cast<const __half*>(S.yss) : nullptr, static_cast<__half*>(out), tokens, A, D);
   return launch_status();
