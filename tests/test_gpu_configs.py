@@ -150,6 +150,29 @@ def test_mixtral_prefill_bf16_small():
     assert max_abs(got, ref) < bf16_abs_bound(ref), (max_abs(got, ref), bf16_abs_bound(ref))
 
 
+@pytest.mark.parametrize("D,Fd,bits", [(1280, 640, [3, 3, 3, 3]), (768, 1920, [3, 1, 3, 4]), (512, 384, [3, 3, 2, 3])])
+def test_decode_three_bit_run_remainders(D, Fd, bits):
+    """One-token layer with 3-bit experts whose reduction lengths leave every remainder of groups
+    in the last 5-group run (10 and 5 groups: none; 6 and 15: one and none; 4 and 3), and packed rows that
+    end inside a 16-row quad: the integer 3-bit path masks rows that straddle two groups and zero-fills
+    rows past the end of the matrix."""
+    layer = MF.make_layer("mixtral", D=D, Fd=Fd, E=4, A=2, bits=bits, seed=21, gate_std=0.02)
+    blk = MF.gpu_block(layer)
+    w1, w3, w2, _ = MF.oracle_parts(layer)
+    for seed in (1, 2):
+        x = torch.randn(1, D, generator=torch.Generator().manual_seed(seed)).half()
+        out, _ = blk(x.cuda().view(1, 1, -1))
+        assert blk.decode_error_code() == 0
+        _, gw, gi = blk._decode(x.cuda(), 0)
+        ref = O.moe_reference_fp32(x, gw.float().cpu(), gi.cpu(), w1, w3, w2)
+        got = out.view(1, -1).float().cpu().numpy()
+        ref = np.asarray(ref, dtype=np.float32)
+        assert rel_fro(got, ref) < REL_FRO_TOL, rel_fro(got, ref)
+        assert max_abs(got, ref) < f16_abs_bound(ref), (max_abs(got, ref), f16_abs_bound(ref))
+        again, _ = blk(x.cuda().view(1, 1, -1))
+        assert torch.equal(out, again)
+
+
 def test_group_gemm_tensor_core_branch():
     """dequant_group_gemm with M >= 32 rows: the tcgen05 GEMM with a device-side expert id and the
     stacked nbits / wq_strides / zs_strides of mixed-bit experts."""
