@@ -1240,7 +1240,7 @@ __device__ __noinline__ float4 drain_slots(float* src, size_t c_total, const uns
 // Two jobs at once (gate and up partials of a column chunk), slot sets given by value: up to
 // four slots of each job are in flight together (one L2 round trip for a strip cut in up to four);
 // each job is summed in slice order.
-__device__ __forceinline__ void drain_pair(float* sa, float* sb, size_t c_total, unsigned ma, unsigned mb, float4& a,
+__device__ __noinline__ void drain_pair(float* sa, float* sb, size_t c_total, unsigned ma, unsigned mb, float4& a,
                                            float4& b) {
   constexpr int kB = 4;
   a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1271,6 +1271,35 @@ __device__ __forceinline__ void drain_pair(float* sa, float* sb, size_t c_total,
       if (qb[i]) { b.x += tb[i].x; b.y += tb[i].y; b.z += tb[i].z; b.w += tb[i].w; __stcg(qb[i], zero); }
     }
   }
+}
+
+// Continue a slice-order sum: add the partial slots of `mask` (up to four loads in flight) and
+// restore them to zero.
+__device__ __noinline__ void drain_more(float* s, size_t c_total, unsigned mask, float4& acc) {
+  constexpr int kB = 4;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  while (mask) {
+    float4* q[kB];
+    float4 t[kB];
+#pragma unroll
+    for (int i = 0; i < kB; ++i) {
+      q[i] = nullptr;
+      if (mask) {
+        q[i] = reinterpret_cast<float4*>(s + static_cast<size_t>(__ffs(mask) - 1) * c_total);
+        mask &= mask - 1;
+        t[i] = __ldcg(q[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kB; ++i)
+      if (q[i]) { acc.x += t[i].x; acc.y += t[i].y; acc.z += t[i].z; acc.w += t[i].w; __stcg(q[i], zero); }
+  }
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ void store_half4(__half* dst, const float4& v) {
@@ -1304,31 +1333,64 @@ __device__ void finisher_role(Smem& S, const FusedParams& P, int* err) {
 
     const bool col_on = 4 * lane < d.ncols;
     const size_t ct = static_cast<size_t>(P.c_total);
-    if (col_on) __stcg(reinterpret_cast<float4*>(P.partial + static_cast<size_t>(d.qa) * ct + d.colp + 4 * lane), r);
+    float4* my_slot = reinterpret_cast<float4*>(P.partial + static_cast<size_t>(d.qa) * ct + d.colp + 4 * lane);
     const int n = d.c * 128 + 4 * lane;
     if (d.phase == 0) {
-      // One 64-bit word per (slot, column chunk): arrivals in the low half, the set of partial
-      // slots in use in the high half (gate: bits 0..15, up: bits 16..31), so that the CTA that
-      // completes the pair learns both from the atomic it has to issue anyway.
-      __threadfence();
-      __syncwarp();
-      unsigned lo = 0, hi = 0;
+      // One 64-bit word per (slot, column chunk): quanta arrived (bits 0..7), quanta whose partial
+      // row is published (bits 8..15), the set of published partial slots (gate: bits 32..47, up:
+      // 48..63).  A part arrives first.  If it is the last to arrive and every other row is already
+      // published (the rule at the end of the gate/up phase, which is what the down phase waits
+      // for), it completes the pair with its own sums still in registers: no store, no fence, no
+      // second round trip on that path.  Otherwise it publishes its row like the others, and
+      // whoever publishes last completes the pair from memory.  Nobody waits for anybody, and the
+      // sums are formed in slice order on either path.
+      const int mine_q = d.qb - d.qa;
+      unsigned long long* c64 = reinterpret_cast<unsigned long long*>(P.counters) + d.ctr;
+      const unsigned long long my_bit = 1ull << (32 + 16 * d.mask + d.qa);
+      unsigned long long word = 0ull;
+      int path = 0;  // 0: not the completer, 1: completes from registers, 2: completes from memory
       if (lane == 0) {
-        unsigned long long* c64 = reinterpret_cast<unsigned long long*>(P.counters) + d.ctr;
-        const unsigned long long mine = 1ull << (32 + 16 * d.mask + d.qa);
-        const unsigned long long old = atomicAdd(c64, static_cast<unsigned long long>(d.qb - d.qa) | mine);
-        lo = static_cast<unsigned>(old) + static_cast<unsigned>(d.qb - d.qa);
-        hi = static_cast<unsigned>((old | mine) >> 32);
-        if (static_cast<int>(lo) == d.expected) *c64 = 0ull;
+        word = atomicAdd(c64, static_cast<unsigned long long>(mine_q));
+        if (static_cast<int>(word & 0xffull) + mine_q == d.expected && static_cast<int>((word >> 8) & 0xffull) == d.expected - mine_q)
+          path = 1;
       }
-      lo = __shfl_sync(0xffffffffu, lo, 0);
-      hi = __shfl_sync(0xffffffffu, hi, 0);
-      if (static_cast<int>(lo) != d.expected) continue;
+      path = __shfl_sync(0xffffffffu, path, 0);
+      if (path == 0) {
+        if (col_on) __stcg(my_slot, r);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          word = atomicAdd(c64, (static_cast<unsigned long long>(mine_q) << 8) | my_bit) | my_bit;
+          if (static_cast<int>((word >> 8) & 0xffull) + mine_q == d.expected) path = 2;
+        }
+        path = __shfl_sync(0xffffffffu, path, 0);
+        if (path == 0) continue;
+      }
+      if (lane == 0) *c64 = 0ull;
+      const unsigned hi = __shfl_sync(0xffffffffu, static_cast<unsigned>(word >> 32), 0);
       __threadfence();
       const SlotInfo& I = S.slot[d.s];
       if (col_on) {
+        float* sa = P.partial + I.colb[0] + n;
+        float* sb = sa + I.F;
+        const unsigned ma = hi & 0xffffu, mb = hi >> 16;
         float4 a, b;
-        drain_pair(P.partial + I.colb[0] + n, P.partial + I.colb[0] + I.F + n, ct, hi & 0xffffu, hi >> 16, a, b);
+        if (path == 2) {
+          drain_pair(sa, sb, ct, ma, mb, a, b);
+        } else {
+          // slots below this part's slice of its own matrix and every slot of the other matrix,
+          // then this part's sums, then the slots above
+          const unsigned below = (1u << d.qa) - 1u;
+          if (d.mask == 0) {
+            drain_pair(sa, sb, ct, ma & below, mb, a, b);
+            a.x += r.x; a.y += r.y; a.z += r.z; a.w += r.w;
+            drain_more(sa, ct, ma & ~below, a);
+          } else {
+            drain_pair(sa, sb, ct, ma, mb & below, a, b);
+            b.x += r.x; b.y += r.y; b.z += r.z; b.w += r.w;
+            drain_more(sb, ct, mb & ~below, b);
+          }
+        }
         a = round_half4(a);
         b = round_half4(b);
         *reinterpret_cast<float4*>(P.h + I.hoff + n) =
@@ -1339,6 +1401,7 @@ __device__ void finisher_role(Smem& S, const FusedParams& P, int* err) {
       if (lane == 0) *reinterpret_cast<volatile int*>(P.counters + 2 * S.pairs_total + d.ctr) = 1;  // h chunk complete
       continue;
     }
+    if (col_on) __stcg(my_slot, r);
     if (P.S <= 2) {
       // Down projections of at most two slots: the slot sets of both (28 bits each, one bit per
       // quantum) ride above an 8-bit arrival count in one 64-bit word per column chunk.
