@@ -23,15 +23,21 @@
 //     it is loaded once per task and used for all eight 16-column tiles.  Two consecutive groups
 //     ride in MMA columns 0..2 and 4..6 and are folded into the fp32 result with their scales and
 //     offsets every two groups.
-//   3-bit: ten codes per word; `word & mask` leaves two codes in the mantissas of an fp16x2
-//     register (subnormals), the A operand of mma.sync.m16n8k16; five groups ride in columns 0..4.
+//   3-bit: ten codes per word at bits 0, 3, .., 27; three masks (one after a shift of the word,
+//     for the two codes that straddle byte boundaries) give u8 operands of the same MMA, five
+//     operand registers per two words.  A run is 64 packed rows = five groups; the group a code
+//     belongs to is a fixed function of the row's position in the run, rows whose codes fall into
+//     two groups are masked per half of the MMA columns, and a group is folded when the 16-row
+//     quad in which it ends is done.
 // The activation tables (digit planes of x for a bit width, of h = silu(x1)*x3 for a slot) are
 // built once per CTA and kept in shared memory.
 // Four finisher warps (parts round robin) add the twelve run lanes of a part and run the
 // cross-CTA protocol: fp32 partial slots that are restored to zero and one 64-bit word per column
-// chunk that carries the arrival count and the set of slots in use, so that the CTA whose
-// atomic completes a chunk knows which slots to add (in slice order: bit-reproducible) and
-// applies the epilogue (h = silu(x1)*x3 in fp32, or the weighted combine).  An h chunk is a
+// chunk that carries the arrival count and the set of slots in use, so that the CTA that
+// completes a chunk knows which slots to add (in slice order: bit-reproducible) and applies the
+// epilogue (h = silu(x1)*x3 in fp32, or the weighted combine).  In the gate/up phase a part
+// arrives before it publishes its row: the part that completes a chunk whose other rows are all
+// published keeps its own sums in registers.  An h chunk is a
 // reduction group of the down projections: a flag per chunk lets a CTA build its phase-1 table
 // group by group while the last gate/up chunks are still being finished, and the weight copies of
 // phase 1 are in flight long before.  Every wait is bounded and records an error code.
