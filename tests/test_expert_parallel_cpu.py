@@ -145,6 +145,24 @@ def test_expert_parallel_with_replicated_experts_gloo():
     assert dict(results) == {0: True, 1: True}
 
 
+def test_expert_parallel_four_ranks_placement_from_row_counts_gloo():
+    """Four ranks, placement computed from the routed-row counts of all ranks' tokens with pieces as
+    small as one row: several experts end up on two or more ranks."""
+    world = 4
+    counts = torch.zeros(E, dtype=torch.int64)
+    for r in range(world):
+        _, _, sel = make_inputs(100 + r, 11 + 3 * r)
+        counts += torch.bincount(sel.reshape(-1), minlength=E)
+    # expert 0 made nine times as popular as it is: the counts only steer the placement, any table gives the same result
+    place = replicated_placement((counts * torch.tensor([9, 1, 1, 1, 1, 1, 1, 1])).tolist(), world, min_rows=1)
+    assert place.max_replicas >= 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 35500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, results, [tuple(i) for i in place.instances]), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True, 2: True, 3: True}
+
+
 def test_rank_with_no_tokens_for_some_experts():
     """A rank may receive zero rows: the plan and the combine still hold."""
     x, w, _ = make_inputs(3, 5)
