@@ -173,6 +173,46 @@ def test_decode_three_bit_run_remainders(D, Fd, bits):
         assert torch.equal(out, again)
 
 
+def test_decode_layer_is_bit_reproducible_over_many_graph_replays():
+    """The cross-CTA sums of the one-launch decode layer are formed in a fixed order whichever
+    CTA completes a chunk: 60 replays of each of six captured layer calls (Mixtral config-1 shape
+    and DeepSeek config-2 shape) give bit-identical outputs, and no wait runs out."""
+    from gemq_b200 import synth
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev).manual_seed(7)
+    cases = [(synth.mixtral_block(seed=100, device=dev), 4096), (synth.mixtral_block(seed=103, device=dev), 4096),
+             (synth.deepseek_block(seed=0, device=dev), 2048)]
+    side = torch.cuda.Stream(device=dev)
+    graphs, keep = [], []  # the graphs read their activations in place: keep them alive
+    with torch.cuda.stream(side):
+        for blk, D in cases:
+            for _ in range(2):
+                x = torch.randn(1, 1, D, device=dev, generator=gen).half()
+                keep.append(x)
+                blk(x)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    o = blk(x)
+                    o = o[0] if isinstance(o, tuple) else o
+                graphs.append((g, o))
+    torch.cuda.synchronize()
+    ref = []
+    for g, o in graphs:
+        g.replay()
+        torch.cuda.synchronize()
+        ref.append(o.clone())
+    bad = torch.zeros((), dtype=torch.int64, device=dev)
+    for _ in range(60):
+        for (g, o), want in zip(graphs, ref):
+            g.replay()
+            bad += (o != want).any().to(torch.int64)
+    torch.cuda.synchronize()
+    assert int(bad) == 0
+    assert all(blk.decode_error_code() == 0 for blk, _ in cases)
+    assert not any(bool(torch.isnan(w).any()) for w in ref)
+
+
 def test_group_gemm_tensor_core_branch():
     """dequant_group_gemm with M >= 32 rows: the tcgen05 GEMM with a device-side expert id and the
     stacked nbits / wq_strides / zs_strides of mixed-bit experts."""
