@@ -540,13 +540,20 @@ def main():
     torch.cuda.synchronize()
     sink = 0.0
 
+    # host side of a step through views of the pinned buffers (numpy float16 views share their memory):
+    # the copy into the staging buffer and the read of the result cost a fraction of a microsecond
+    # instead of several tensor-method calls
+    xh_np = [t.view(-1).numpy() for t in xh]
+    in_np, out_np = stage_in.view(-1).numpy(), stage_out.view(-1).numpy()
+    cur = torch.cuda.current_stream()
+
     def e2e_steps(n):
         nonlocal sink
         for i in range(n):
-            stage_in.copy_(xh[i % n_x])
+            in_np[:] = xh_np[i % n_x]
             e2e_graphs[i % L].replay()
-            torch.cuda.current_stream().synchronize()
-            sink += float(stage_out[0, 0, 0])
+            cur.synchronize()
+            sink += float(out_np[0])
 
     e2e_steps(max(3, args.warmup // 4))
     if world > 1:
