@@ -844,12 +844,19 @@ __device__ __forceinline__ void loader_step(Loader& L, const Smem& S, int kq, in
     } else {
       const int quad = L.i / 5, qpos = L.i - 5 * quad;  // position in the quad sequence
       if (qpos < 4) {
-        // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
-        const uint32_t* src = L.rows_left > 0 ? L.w : S.parts[L.p].w + 4 * lane;
+        if (L.rows_left >= 4) {
+          const char* src = reinterpret_cast<const char*>(L.w);
+          const size_t pitch = static_cast<size_t>(L.N) * 4;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          cp_async16s(dst + L.roff[r], src, r < L.rows_left ? 16 : 0);
-          if (r < 3 && r + 1 < L.rows_left) src += L.N;
+          for (int r = 0; r < 4; ++r) cp_async16(dst + L.roff[r], src + r * pitch);
+        } else {
+          // rows past the end of a 3-bit matrix are zero-filled; their source stays on the last valid row
+          const uint32_t* src = L.rows_left > 0 ? L.w : S.parts[L.p].w + 4 * lane;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            cp_async16s(dst + L.roff[r], src, r < L.rows_left ? 16 : 0);
+            if (r < 3 && r + 1 < L.rows_left) src += L.N;
+          }
         }
         L.rows_left -= 4;
         L.w += 4 * static_cast<size_t>(L.N);
