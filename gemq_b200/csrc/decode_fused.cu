@@ -542,16 +542,15 @@ __device__ void route_cta(Smem& S, const FusedParams& P) {
   if (lane >= E) p = -1.f;
   float my_w = 0.f;
   int my_i = 0;
+  // top-k: the largest probability, the lowest expert id among equals.  Probabilities are >= +0,
+  // so their bit patterns order like unsigned integers: one warp-wide integer max and one ballot per
+  // pick instead of a shuffle tree over (value, index) pairs.
 #pragma unroll 1
   for (int a = 0; a < A; ++a) {
-    float bv = p > -2.f ? p : -2.f;
-    int bi = p > -2.f ? lane : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
+    const unsigned key = p >= 0.f ? __float_as_uint(p) + 1u : 0u;  // 0: not a candidate (beyond E, or taken)
+    const unsigned kmax = __reduce_max_sync(0xffffffffu, key);
+    const int bi = __ffs(__ballot_sync(0xffffffffu, key == kmax)) - 1;
+    const float bv = __uint_as_float(kmax - 1u);
     if (lane == a) { my_w = bv; my_i = bi; }
     if (lane == bi) p = -3.f;
   }
